@@ -1,0 +1,140 @@
+// Shared device/host helpers for the geoweave_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/geoweave_b200.h"
+
+namespace gw {
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+extern thread_local int g_last_cuda_error;
+
+inline int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return GW_ERR_CUDA;
+}
+
+#define GW_CUDA_TRY(expr)                          \
+  do {                                             \
+    cudaError_t _e = (expr);                       \
+    if (_e != cudaSuccess) return gw::cuda_fail(_e); \
+  } while (0)
+
+#define GW_LAUNCH_CHECK() GW_CUDA_TRY(cudaGetLastError())
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t dtype_size(int dtype) { return dtype == GW_F32 ? 4 : 2; }
+inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// ---------------------------------------------------------------------------------------------
+// element conversion
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+
+// two packed 16-bit elements -> two floats
+template <typename T> __device__ __forceinline__ void unpack2(uint32_t u, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t u, float& lo, float& hi) {
+  lo = __uint_as_float(u << 16);
+  hi = __uint_as_float(u & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void unpack2<__half>(uint32_t u, float& lo, float& hi) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u));
+  lo = f.x;
+  hi = f.y;
+}
+
+// ---------------------------------------------------------------------------------------------
+// ordering keys: larger score -> larger 32-bit key.  -0.0 is folded onto +0.0 so the two tie.
+// A candidate is ranked by the 64-bit composite (key << 32 | ~index): descending composite order is
+// (score descending, index ascending), which is the selection rule of the whole library.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t score_key(float f) {
+  const uint32_t u = __float_as_uint(__fadd_rn(f, 0.0f));
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_score(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+__device__ __forceinline__ unsigned long long composite(uint32_t key, uint32_t idx) {
+  return (static_cast<unsigned long long>(key) << 32) | static_cast<unsigned long long>(~idx);
+}
+__device__ __forceinline__ uint32_t composite_key(unsigned long long c) { return static_cast<uint32_t>(c >> 32); }
+__device__ __forceinline__ uint32_t composite_idx(unsigned long long c) { return ~static_cast<uint32_t>(c); }
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers: shared-memory addresses, mbarriers, bulk (TMA) copies.  Every wait is bounded.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Wait for a phase of an mbarrier, for at most ~2 s of wall time.  Returns false when the wait ran out;
+// the caller records GW_ERR_TIMEOUT in the status word and leaves its loop (no trap, no endless spin).
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+  }
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.  Both addresses 16-byte
+// aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ void report_status(int* status_dev, int code) {
+  if (status_dev != nullptr) atomicCAS(status_dev, 0, code);
+}
+
+}  // namespace gw

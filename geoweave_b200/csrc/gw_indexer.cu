@@ -1,0 +1,758 @@
+// Stage 1+2: indexer score on tcgen05 tensor cores with the exact top-k kept in the epilogue.
+//
+//   score[t,s] = sum_h w[s,h] * relu(scale * <q[t,h,:], k[s,h,:]>)            q,k bf16/fp16, fp32 accumulate
+//
+// One CTA owns a block of 128 query rows and walks all keys in tiles of 64.  Per tile and indexer head one
+// 128x64x64 product is issued as four tcgen05.mma (K=16 each) from shared-memory operands that TMA loaded
+// with the 128-byte swizzle; the Hi accumulators of a tile sit side by side in tensor memory, and two such
+// sets (2 x 256 columns) alternate so the tensor cores work on tile j+1 while tile j is being reduced.
+//
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..9 = epilogue.
+// Epilogue thread = one query row (its TMEM lane); the eight warps form two streams of four, stream p
+// reduces the tiles held in accumulator set p.  A thread reads its row of the accumulators with
+// tcgen05.ld, forms the score, and appends (score, key) to its row's candidate list in global memory when
+// score >= tau, tau being a per-row lower bound on the final k-th score.  Whenever a list is nearly full the
+// warp compacts it to its exact top-k (gw_select.cuh) and raises tau to just above the new k-th score.  After
+// the last tile the two streams' lists of a row are merged by one more exact selection, which writes the
+// result.  The N x N score matrix never exists in memory.
+//
+// tau starts from a sampled estimate when the key set is large: scores against every `step`-th key are
+// written densely by the same main loop (score mode), a small kernel takes their r-th largest per row, r
+// chosen so that about 2k keys pass.  The estimate is only a filter: a row that ends with fewer than k
+// candidates is redone from tau = -inf by a second launch that normally finds an empty work list, so the
+// result is exact whatever the data.
+#include <cuda.h>
+#include <math.h>
+
+#include "gw_common.cuh"
+#include "gw_select.cuh"
+
+namespace gw {
+namespace {
+
+constexpr int BM = 128;           // query rows per CTA (TMEM lanes)
+constexpr int BN = 64;            // keys per tile
+constexpr int DI = 64;            // indexer head dim = one 128-byte swizzle atom of bf16
+constexpr int NSTG = 3;           // key-tile ring depth
+constexpr int EPI_WARPS = 8;
+constexpr int NTHREADS = 64 + EPI_WARPS * 32;
+constexpr int ACC_COLS = 256;     // TMEM columns per accumulator set (Hi * BN <= 256)
+constexpr int TMEM_COLS = 512;
+constexpr int SEL_BINS = 1024;
+constexpr int Q_HEAD_BYTES = BM * DI * 2;   // 16 KB
+constexpr int K_HEAD_BYTES = BN * DI * 2;   // 8 KB
+constexpr int MAX_SLOTS = 160;    // upper bound on resident CTAs (one per SM)
+
+enum { MODE_TOPK = 0, MODE_SCORES = 1 };
+
+struct IdxParams {
+  const float4* wsc;       // [S_pad] w * scale, four floats per key (heads beyond Hi are 0)
+  const float* tau_in;     // [T] initial thresholds, or null for -inf
+  int32_t* out_idx;        // [T,k]
+  void* out_scores;        // [T,k] of out_dtype, nullable
+  int out_dtype;
+  float* dense_out;        // score mode: [T, S] with row stride dense_stride
+  int64_t dense_stride;
+  uint2* cand;             // [slots][BM][2][caph] (score bits, key index)
+  int caph;
+  int T, S, k;
+  int key_step;            // score mode: column j is key j * key_step
+  const int* block_list;   // redo launch: row blocks to process ...
+  const int* block_count;  // ... and how many; null = all blocks
+  int* redo_count;         // first launch: rows that ended short are reported here
+  int* redo_list;
+  float* tau_redo;         // [T] -inf for rows to redo, +inf for finished rows
+  int* status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05 / TMA wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);        // start address
+  d |= static_cast<uint64_t>(1) << 16;                         // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                 // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                         // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                         // 128-byte swizzle
+  return d;
+}
+// kind::f16 instruction descriptor: fp32 accumulate, A and B K-major, M=128, N=64
+__host__ __device__ constexpr uint32_t make_idesc(int ab_format) {
+  return (1u << 4) | (static_cast<uint32_t>(ab_format) << 7) | (static_cast<uint32_t>(ab_format) << 10) |
+         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+struct TwoSegSrc {
+  const uint2* a;
+  const uint2* b;
+  int na;
+  __device__ __forceinline__ unsigned long long operator()(int i) const {
+    const uint2 e = (i < na) ? a[i] : b[i - na];
+    return composite(score_key(__uint_as_float(e.x)), e.y);
+  }
+};
+struct CompactSink {  // in-place: the survivors move to the front of the same list
+  uint2* dst;
+  __device__ __forceinline__ void operator()(int pos, unsigned long long c) const {
+    dst[pos] = make_uint2(__float_as_uint(key_score(composite_key(c))), composite_idx(c));
+  }
+};
+struct FinalSink {
+  int32_t* oi;
+  void* os;
+  int dtype;
+  __device__ __forceinline__ void operator()(int pos, unsigned long long c) const {
+    oi[pos] = static_cast<int32_t>(composite_idx(c));
+    if (os != nullptr) {
+      const float s = key_score(composite_key(c));
+      if (dtype == GW_BF16) static_cast<__nv_bfloat16*>(os)[pos] = __float2bfloat16_rn(s);
+      else if (dtype == GW_F16) static_cast<__half*>(os)[pos] = __float2half_rn(s);
+      else static_cast<float*>(os)[pos] = s;
+    }
+  }
+};
+
+struct alignas(8) IdxShared {
+  uint64_t q_full, q_empty;
+  uint64_t k_full[NSTG], k_empty[NSTG];
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  int block_failed;
+  int cnt[2][BM];
+  float smin[2][BM];
+  float smax[2][BM];
+};
+
+template <int HI, int MODE>
+__global__ void __launch_bounds__(NTHREADS, 1)
+indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const IdxParams p,
+               const uint32_t idesc) {
+  extern __shared__ unsigned char smem_raw[];
+  // operand tiles need 1024-byte alignment for the 128-byte swizzle
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* q_smem = smem;                                  // HI x 16 KB
+  unsigned char* k_smem = q_smem + HI * Q_HEAD_BYTES;            // NSTG x HI x 8 KB
+  SelectSmem<SEL_BINS>* sel = reinterpret_cast<SelectSmem<SEL_BINS>*>(k_smem + NSTG * HI * K_HEAD_BYTES);
+  IdxShared* sh = reinterpret_cast<IdxShared*>(sel + EPI_WARPS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblocks_all = (p.T + BM - 1) / BM;
+  const int nwork = (p.block_count != nullptr) ? *p.block_count : nblocks_all;
+  const int ntiles = (p.S + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sh->q_full, 1);
+    mbar_init(&sh->q_empty, 1);
+    for (int s = 0; s < NSTG; ++s) {
+      mbar_init(&sh->k_full[s], 1);
+      mbar_init(&sh->k_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh->acc_full[b], 1);
+      mbar_init(&sh->acc_empty[b], 4);
+    }
+    sh->abort_flag = 0;
+    sh->block_failed = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) tmem_alloc(&sh->tmem_base, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t kuse = 0, nblk = 0;
+      for (int wi = blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x, ++nblk) {
+        const int rb = p.block_list ? p.block_list[wi] : wi;
+        if (!mbar_wait_bounded(&sh->q_empty, (nblk & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+        mbar_arrive_expect_tx(&sh->q_full, HI * Q_HEAD_BYTES);
+#pragma unroll
+        for (int h = 0; h < HI; ++h) tma_load_2d(q_smem + h * Q_HEAD_BYTES, &tmQ, h * DI, rb * BM, &sh->q_full);
+        for (int j = 0; j < ntiles; ++j, ++kuse) {
+          const uint32_t s = kuse % NSTG, n = kuse / NSTG;
+          if (!mbar_wait_bounded(&sh->k_empty[s], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          if (sh->abort_flag) break;
+          mbar_arrive_expect_tx(&sh->k_full[s], HI * K_HEAD_BYTES);
+#pragma unroll
+          for (int h = 0; h < HI; ++h)
+            tma_load_2d(k_smem + (s * HI + h) * K_HEAD_BYTES, &tmK, h * DI, j * BN, &sh->k_full[s]);
+        }
+      }
+      if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      uint32_t kuse = 0, nblk = 0, use0 = 0, use1 = 0;
+      for (int wi = blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x, ++nblk) {
+        if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
+        for (int j = 0; j < ntiles; ++j, ++kuse) {
+          const uint32_t b = j & 1;
+          const uint32_t n = b ? use1 : use0;
+          if (!mbar_wait_bounded(&sh->acc_empty[b], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          const uint32_t s = kuse % NSTG;
+          if (!mbar_wait_bounded(&sh->k_full[s], (kuse / NSTG) & 1u)) { sh->abort_flag = 1; break; }
+          if (sh->abort_flag) break;
+          tc_fence_after();
+#pragma unroll
+          for (int h = 0; h < HI; ++h) {
+            const uint64_t adesc = make_smem_desc(smem_u32(q_smem + h * Q_HEAD_BYTES));
+            const uint64_t bdesc = make_smem_desc(smem_u32(k_smem + (s * HI + h) * K_HEAD_BYTES));
+            const uint32_t d = tmem_base + b * ACC_COLS + h * BN;
+#pragma unroll
+            for (int kk = 0; kk < DI / 16; ++kk)  // +32 bytes along K per step = +2 in the address field
+              tc_mma_f16(d, adesc + 2 * kk, bdesc + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(&sh->k_empty[s]);
+          tc_commit(&sh->acc_full[b]);
+          if (b) ++use1; else ++use0;
+        }
+        tc_commit(&sh->q_empty);
+      }
+      if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int e = warp - 2;
+    const int strm = e >> 2;          // which accumulator set / candidate stream
+    const int lq = warp & 3;          // TMEM lane quarter this warp may read
+    const int row_in_tile = lq * 32 + lane;
+    const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + strm * ACC_COLS;
+    uint32_t acc_use = 0;
+    uint2* const mybuf = (MODE == MODE_TOPK)
+                             ? p.cand + ((static_cast<size_t>(blockIdx.x) * BM + row_in_tile) * 2 + strm) * p.caph
+                             : nullptr;
+    const int compact_at = p.caph - BN;
+
+    for (int wi = blockIdx.x; wi < nwork; wi += gridDim.x) {
+      const int rb = p.block_list ? p.block_list[wi] : wi;
+      const int row = rb * BM + row_in_tile;
+      float tau = INFINITY;
+      if (row < p.T) tau = p.tau_in ? p.tau_in[row] : -INFINITY;
+      const bool active = tau < INFINITY;
+      int cnt = 0;
+      float smin = INFINITY, smax = -INFINITY;
+
+      for (int j = strm; j < ntiles; j += 2) {
+        if (sh->abort_flag) break;
+        if (!mbar_wait_bounded(&sh->acc_full[strm], acc_use & 1u)) { sh->abort_flag = 1; break; }
+        tc_fence_after();
+        const int col_base = j * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t a[HI][16];
+#pragma unroll
+          for (int h = 0; h < HI; ++h) tmem_ld_x16(taddr_row + h * BN + c0, a[h]);
+          tmem_wait_ld();
+          float sc[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const int col = col_base + c0 + c;
+            const float4 w4 = __ldg(p.wsc + static_cast<size_t>(col) * p.key_step);
+            float s = 0.f;
+            s = fmaf(fmaxf(__uint_as_float(a[0][c]), 0.f), w4.x, s);
+            if (HI > 1) s = fmaf(fmaxf(__uint_as_float(a[1 % HI][c]), 0.f), w4.y, s);
+            if (HI > 2) s = fmaf(fmaxf(__uint_as_float(a[2 % HI][c]), 0.f), w4.z, s);
+            if (HI > 3) s = fmaf(fmaxf(__uint_as_float(a[3 % HI][c]), 0.f), w4.w, s);
+            sc[c] = s;
+          }
+          if (MODE == MODE_TOPK) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int col = col_base + c0 + c;
+              if (sc[c] >= tau && col < p.S) {
+                mybuf[cnt] = make_uint2(__float_as_uint(sc[c]), static_cast<uint32_t>(col));
+                ++cnt;
+                smin = fminf(smin, sc[c]);
+                smax = fmaxf(smax, sc[c]);
+              }
+            }
+          } else if (row < p.T) {
+            float* orow = p.dense_out + static_cast<int64_t>(row) * p.dense_stride + col_base + c0;
+            if (col_base + c0 + 16 <= p.S && (p.dense_stride & 3) == 0) {
+#pragma unroll
+              for (int c = 0; c < 16; c += 4)
+                *reinterpret_cast<float4*>(orow + c) = make_float4(sc[c], sc[c + 1], sc[c + 2], sc[c + 3]);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 16; ++c)
+                if (col_base + c0 + c < p.S) orow[c] = sc[c];
+            }
+          }
+        }
+        // hand the accumulator set back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->acc_empty[strm]);
+        ++acc_use;
+
+        if (MODE == MODE_TOPK) {
+          // lists that could overflow during the next tile are cut back to their exact top-k now
+          uint32_t need = __ballot_sync(0xffffffffu, cnt > compact_at);
+          while (need) {
+            const int r = __ffs(need) - 1;
+            need &= need - 1;
+            uint2* buf = reinterpret_cast<uint2*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(mybuf), r));
+            const int n = __shfl_sync(0xffffffffu, cnt, r);
+            const float lo_s = __shfl_sync(0xffffffffu, smin, r);
+            const float hi_s = __shfl_sync(0xffffffffu, smax, r);
+            __syncwarp();
+            TwoSegSrc src{buf, buf, n};
+            CompactSink sink{buf};
+            unsigned long long kth = 0;
+            const int kept = group_select_topk<32, SEL_BINS>(
+                src, n, p.k, composite(score_key(lo_s), 0xffffffffu), composite(score_key(hi_s), 0u), sel[e], lane, 0,
+                sink, &kth);
+            if (lane == r && n > p.k) {
+              cnt = kept;
+              const uint32_t kk = composite_key(kth);
+              smin = key_score(kk);
+              tau = key_score(kk + 1u);  // later keys have larger indices: only a strictly larger score can enter
+            }
+            __syncwarp();
+          }
+        }
+      }
+
+      if (MODE == MODE_TOPK) {
+        sh->cnt[strm][row_in_tile] = active ? cnt : -1;
+        sh->smin[strm][row_in_tile] = smin;
+        sh->smax[strm][row_in_tile] = smax;
+        named_bar_sync(1, EPI_WARPS * 32);
+        // merge the two streams of each row: exact top-k of their union
+        for (int r = e; r < BM; r += EPI_WARPS) {
+          const int n0 = sh->cnt[0][r], n1 = sh->cnt[1][r];
+          const int grow = rb * BM + r;
+          if (n0 < 0 || grow >= p.T || sh->abort_flag) continue;
+          const int n = n0 + n1;
+          if (n < p.k) {  // the sampled threshold was too high for this row: redo it from -inf
+            if (lane == 0) {
+              sh->block_failed = 1;
+              if (p.tau_redo) p.tau_redo[grow] = -INFINITY;
+            }
+            continue;
+          }
+          if (lane == 0 && p.tau_redo) p.tau_redo[grow] = INFINITY;
+          const uint2* b0 = p.cand + ((static_cast<size_t>(blockIdx.x) * BM + r) * 2 + 0) * p.caph;
+          const uint2* b1 = b0 + p.caph;
+          const float lo_s = fminf(sh->smin[0][r], sh->smin[1][r]);
+          const float hi_s = fmaxf(sh->smax[0][r], sh->smax[1][r]);
+          TwoSegSrc src{b0, b1, n0};
+          FinalSink sink{p.out_idx + static_cast<int64_t>(grow) * p.k,
+                         p.out_scores ? static_cast<unsigned char*>(p.out_scores) +
+                                            static_cast<int64_t>(grow) * p.k * (p.out_dtype == GW_F32 ? 4 : 2)
+                                      : nullptr,
+                         p.out_dtype};
+          group_select_topk<32, SEL_BINS>(src, n, p.k, composite(score_key(lo_s), 0xffffffffu),
+                                          composite(score_key(hi_s), 0u), sel[e], lane, 0, sink, nullptr);
+        }
+        named_bar_sync(1, EPI_WARPS * 32);
+        if (e == 0 && lane == 0 && sh->block_failed) {
+          sh->block_failed = 0;
+          if (p.redo_count) {
+            const int pos = atomicAdd(p.redo_count, 1);
+            p.redo_list[pos] = rb;
+          }
+        }
+      }
+      if (sh->abort_flag) break;
+    }
+    if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// w * scale as fp32, four per key; rows beyond S (tile padding) are zero
+template <typename T>
+__global__ void prep_w_kernel(const T* w, int S, int Hi, float scale, float4* wsc, int s_pad) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= s_pad) return;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (s < S)
+    for (int h = 0; h < Hi; ++h) v[h] = to_float(w[static_cast<size_t>(s) * Hi + h]) * scale;
+  wsc[s] = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+// r-th largest of each dense row -> tau (one warp per row)
+struct DenseF32Src {
+  const float* row;
+  __device__ __forceinline__ unsigned long long operator()(int i) const {
+    return composite(score_key(row[i]), static_cast<uint32_t>(i));
+  }
+};
+struct NullSink {
+  __device__ __forceinline__ void operator()(int, unsigned long long) const {}
+};
+constexpr int KTH_WARPS = 8;
+__global__ void __launch_bounds__(KTH_WARPS * 32) kth_rows_kernel(const float* sc, int m, int64_t stride, int T, int r,
+                                                                  float* tau) {
+  __shared__ SelectSmem<SEL_BINS> sm[KTH_WARPS];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * KTH_WARPS + w;
+  if (row >= T) return;
+  DenseF32Src src{sc + static_cast<int64_t>(row) * stride};
+  uint32_t kmin = 0xffffffffu, kmax = 0u;
+  for (int i = lane; i < m; i += 32) {
+    const uint32_t key = score_key(src.row[i]);
+    kmin = min(kmin, key);
+    kmax = max(kmax, key);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, d));
+    kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, d));
+  }
+  unsigned long long kth = 0;
+  group_select_topk<32, SEL_BINS>(src, m, r, static_cast<unsigned long long>(kmin) << 32,
+                                  (static_cast<unsigned long long>(kmax) << 32) | 0xffffffffull, sm[w], lane, 0,
+                                  NullSink{}, &kth);
+  if (lane == 0) tau[row] = key_score(composite_key(kth));
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess) return (EncodeTiledFn) nullptr;
+    return q == cudaDriverEntryPointSuccess ? reinterpret_cast<EncodeTiledFn>(ptr) : (EncodeTiledFn) nullptr;
+  }();
+  return fn;
+}
+
+// rows x (Hi*64) 16-bit matrix, row pitch `pitch_bytes`; box = 64 columns x box_rows, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, int Hi, int64_t pitch_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return GW_ERR_CUDA;
+  const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(Hi) * DI, static_cast<cuuint64_t>(rows)};
+  const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(pitch_bytes)};
+  const cuuint32_t box[2] = {DI, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, dtype == GW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                        const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return GW_ERR_CUDA;
+  }
+  return GW_OK;
+}
+
+size_t smem_bytes(int Hi) {
+  return 1024 + static_cast<size_t>(Hi) * Q_HEAD_BYTES + static_cast<size_t>(NSTG) * Hi * K_HEAD_BYTES +
+         EPI_WARPS * sizeof(SelectSmem<SEL_BINS>) + sizeof(IdxShared);
+}
+
+int device_info(int* sms) {
+  int dev = 0, major = 0;
+  GW_CUDA_TRY(cudaGetDevice(&dev));
+  GW_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  GW_CUDA_TRY(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+  return major == 10 ? GW_OK : GW_ERR_NO_SM100;
+}
+
+template <int MODE>
+int launch_indexer(int Hi, const CUtensorMap& mq, const CUtensorMap& mk, const IdxParams& p, uint32_t idesc, int grid,
+                   cudaStream_t st) {
+  const size_t smem = smem_bytes(Hi);
+#define GW_IDX_CASE(H)                                                                                          \
+  case H: {                                                                                                     \
+    auto kern = indexer_kernel<H, MODE>;                                                                        \
+    GW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))); \
+    kern<<<grid, NTHREADS, smem, st>>>(mq, mk, p, idesc);                                                       \
+    break;                                                                                                      \
+  }
+  switch (Hi) {
+    GW_IDX_CASE(1)
+    GW_IDX_CASE(2)
+    GW_IDX_CASE(3)
+    GW_IDX_CASE(4)
+    default: return GW_ERR_UNSUPPORTED;
+  }
+#undef GW_IDX_CASE
+  GW_LAUNCH_CHECK();
+  return GW_OK;
+}
+
+int launch_prep_w(const void* w, int dtype, int S, int Hi, float scale, float4* wsc, int s_pad, cudaStream_t st) {
+  const int thr = 256, grid = (s_pad + thr - 1) / thr;
+  if (dtype == GW_BF16)
+    prep_w_kernel<__nv_bfloat16><<<grid, thr, 0, st>>>(static_cast<const __nv_bfloat16*>(w), S, Hi, scale, wsc, s_pad);
+  else
+    prep_w_kernel<__half><<<grid, thr, 0, st>>>(static_cast<const __half*>(w), S, Hi, scale, wsc, s_pad);
+  GW_LAUNCH_CHECK();
+  return GW_OK;
+}
+
+// sampling plan for the initial threshold
+struct SamplePlan {
+  int step;  // 0 = no sampling
+  int m;     // sampled keys
+  int rank;  // tau = rank-th largest sampled score
+};
+SamplePlan plan_sample(int S, int k) {
+  SamplePlan sp{0, 0, 0};
+  if (S < 4096 || static_cast<int64_t>(S) < 8ll * k) return sp;
+  int step = S / 1024;
+  if (step < 2) return sp;
+  step |= 1;  // odd: never in lock-step with an even token grid
+  const int m = (S + step - 1) / step;
+  const double ratio = static_cast<double>(k) / step;
+  const int rank = static_cast<int>(ceil(ratio + 6.0 * sqrt(ratio) + 2.0));
+  if (rank * 2 >= m) return sp;
+  sp.step = step;
+  sp.m = m;
+  sp.rank = rank;
+  return sp;
+}
+
+int cand_capacity(int k) {
+  int c = 2 * k;
+  if (c < 1024) c = 1024;
+  return static_cast<int>(round_up(static_cast<size_t>(c), 64));
+}
+
+struct WsLayout {
+  size_t wsc, tau0, tau_redo, redo, sample, cand, total;
+  int s_pad, m_pad, slots, caph;
+};
+WsLayout ws_layout(int T, int S, int k) {
+  WsLayout L;
+  const int nblocks = (T + BM - 1) / BM;
+  const SamplePlan sp = plan_sample(S, k);
+  // the sampled pass reads w at key j*step for j up to the end of its last tile
+  L.s_pad = static_cast<int>(round_up(static_cast<size_t>(S), BN)) + BN * (sp.step > 1 ? sp.step : 1) + BN;
+  L.slots = nblocks < MAX_SLOTS ? nblocks : MAX_SLOTS;
+  L.caph = cand_capacity(k);
+  L.m_pad = static_cast<int>(round_up(static_cast<size_t>(sp.m), 4));
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t at = off;
+    off += round_up(bytes, 256);
+    return at;
+  };
+  L.wsc = take(static_cast<size_t>(L.s_pad) * 16);
+  L.tau0 = take(static_cast<size_t>(T) * 4);
+  L.tau_redo = take(static_cast<size_t>(T) * 4);
+  L.redo = take(static_cast<size_t>(nblocks + 1) * 4);
+  L.sample = take(static_cast<size_t>(T) * L.m_pad * 4);
+  L.cand = take(static_cast<size_t>(L.slots) * BM * 2 * L.caph * 8);
+  L.total = off;
+  return L;
+}
+
+int check_common(const void* q, const void* k, const void* w, int dtype, int B, int T, int S, int Hi, int Di) {
+  if (!q || !k || !w || B <= 0 || T < 0 || S <= 0 || Hi <= 0 || Di <= 0) return GW_ERR_INVALID_ARG;
+  if (dtype != GW_BF16 && dtype != GW_F16) return GW_ERR_UNSUPPORTED;
+  if (Di != DI || Hi > 4) return GW_ERR_UNSUPPORTED;
+  if (!aligned16(q) || !aligned16(k)) return GW_ERR_INVALID_ARG;
+  return GW_OK;
+}
+
+}  // namespace
+}  // namespace gw
+
+using namespace gw;
+
+extern "C" size_t gw_indexer_topk_workspace_bytes(int B, int T, int S, int Hi, int Di, int k) {
+  (void)B; (void)Hi; (void)Di;
+  if (T <= 0 || S <= 0 || k <= 0) return 0;
+  return ws_layout(T, S, k).total;
+}
+
+extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
+                                 int Hi, int Di, float scale, int key_step, float* out, int64_t out_row_stride,
+                                 int* status_dev, gw_stream_t stream) {
+  int rc = check_common(q_idx, k_idx, w, dtype, B, T, S, Hi, Di);
+  if (rc != GW_OK) return rc;
+  if (!out || key_step <= 0) return GW_ERR_INVALID_ARG;
+  const int m = (S + key_step - 1) / key_step;
+  if (out_row_stride < m) return GW_ERR_INVALID_ARG;
+  if (T == 0) return GW_OK;
+  int sms = 0;
+  rc = device_info(&sms);
+  if (rc != GW_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // this debug/verification entry owns a small scratch for w*scale (stream-ordered allocation)
+  const int s_pad = static_cast<int>(round_up(static_cast<size_t>(S), BN)) + BN * key_step + BN;
+  float4* wsc = nullptr;
+  GW_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&wsc), static_cast<size_t>(s_pad) * 16, st));
+  const size_t row_bytes = static_cast<size_t>(Hi) * DI * 2;
+  const int nblocks = (T + BM - 1) / BM;
+  const int grid = nblocks < sms ? nblocks : sms;
+  for (int b = 0; b < B && rc == GW_OK; ++b) {
+    const unsigned char* qb = static_cast<const unsigned char*>(q_idx) + static_cast<size_t>(b) * T * row_bytes;
+    const unsigned char* kb = static_cast<const unsigned char*>(k_idx) + static_cast<size_t>(b) * S * row_bytes;
+    const unsigned char* wb = static_cast<const unsigned char*>(w) + static_cast<size_t>(b) * S * Hi * 2;
+    rc = launch_prep_w(wb, dtype, S, Hi, scale, wsc, s_pad, st);
+    if (rc != GW_OK) break;
+    CUtensorMap mq, mk;
+    rc = make_map(&mq, qb, dtype, T, Hi, row_bytes, BM);
+    if (rc != GW_OK) break;
+    rc = make_map(&mk, kb, dtype, m, Hi, row_bytes * key_step, BN);
+    if (rc != GW_OK) break;
+    IdxParams p{};
+    p.wsc = wsc;
+    p.dense_out = out + static_cast<int64_t>(b) * T * out_row_stride;
+    p.dense_stride = out_row_stride;
+    p.T = T;
+    p.S = m;
+    p.k = 0;
+    p.key_step = key_step;
+    p.status = status_dev;
+    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc(dtype == GW_BF16 ? 1 : 0), grid, st);
+  }
+  const cudaError_t fe = cudaFreeAsync(wsc, st);
+  if (rc == GW_OK && fe != cudaSuccess) return cuda_fail(fe);
+  return rc;
+}
+
+extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
+                                     int Hi, int Di, float scale, int k, int32_t* out_idx, void* out_scores,
+                                     void* workspace, size_t workspace_bytes, int* status_dev, gw_stream_t stream) {
+  int rc = check_common(q_idx, k_idx, w, dtype, B, T, S, Hi, Di);
+  if (rc != GW_OK) return rc;
+  if (!out_idx || k <= 0 || k > S) return GW_ERR_INVALID_ARG;
+  if (T == 0) return GW_OK;
+  const WsLayout L = ws_layout(T, S, k);
+  if (!workspace || workspace_bytes < L.total) return GW_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return GW_ERR_INVALID_ARG;
+  int sms = 0;
+  rc = device_info(&sms);
+  if (rc != GW_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  float4* wsc = reinterpret_cast<float4*>(ws + L.wsc);
+  float* tau0 = reinterpret_cast<float*>(ws + L.tau0);
+  float* tau_redo = reinterpret_cast<float*>(ws + L.tau_redo);
+  int* redo = reinterpret_cast<int*>(ws + L.redo);
+  float* sample = reinterpret_cast<float*>(ws + L.sample);
+  uint2* cand = reinterpret_cast<uint2*>(ws + L.cand);
+
+  const SamplePlan sp = plan_sample(S, k);
+  const size_t row_bytes = static_cast<size_t>(Hi) * DI * 2;
+  const int nblocks = (T + BM - 1) / BM;
+  int grid = nblocks < sms ? nblocks : sms;
+  if (grid > L.slots) grid = L.slots;
+  const uint32_t idesc = make_idesc(dtype == GW_BF16 ? 1 : 0);
+  const size_t out_es = dtype_size(dtype);
+
+  for (int b = 0; b < B; ++b) {
+    const unsigned char* qb = static_cast<const unsigned char*>(q_idx) + static_cast<size_t>(b) * T * row_bytes;
+    const unsigned char* kb = static_cast<const unsigned char*>(k_idx) + static_cast<size_t>(b) * S * row_bytes;
+    const unsigned char* wb = static_cast<const unsigned char*>(w) + static_cast<size_t>(b) * S * Hi * 2;
+    rc = launch_prep_w(wb, dtype, S, Hi, scale, wsc, L.s_pad, st);
+    if (rc != GW_OK) return rc;
+    CUtensorMap mq, mk;
+    rc = make_map(&mq, qb, dtype, T, Hi, row_bytes, BM);
+    if (rc != GW_OK) return rc;
+
+    if (sp.step > 0) {
+      // threshold estimate: dense scores against every step-th key, then their rank-th largest per row
+      CUtensorMap ms;
+      rc = make_map(&ms, kb, dtype, sp.m, Hi, row_bytes * sp.step, BN);
+      if (rc != GW_OK) return rc;
+      IdxParams ps{};
+      ps.wsc = wsc;
+      ps.dense_out = sample;
+      ps.dense_stride = L.m_pad;
+      ps.T = T;
+      ps.S = sp.m;
+      ps.key_step = sp.step;
+      ps.status = status_dev;
+      rc = launch_indexer<MODE_SCORES>(Hi, mq, ms, ps, idesc, grid, st);
+      if (rc != GW_OK) return rc;
+      kth_rows_kernel<<<(T + KTH_WARPS - 1) / KTH_WARPS, KTH_WARPS * 32, 0, st>>>(sample, sp.m, L.m_pad, T, sp.rank, tau0);
+      GW_LAUNCH_CHECK();
+    }
+
+    rc = make_map(&mk, kb, dtype, S, Hi, row_bytes, BN);
+    if (rc != GW_OK) return rc;
+    GW_CUDA_TRY(cudaMemsetAsync(redo, 0, 4, st));
+    IdxParams p{};
+    p.wsc = wsc;
+    p.tau_in = sp.step > 0 ? tau0 : nullptr;
+    p.out_idx = out_idx + static_cast<int64_t>(b) * T * k;
+    p.out_scores = out_scores ? static_cast<unsigned char*>(out_scores) + static_cast<size_t>(b) * T * k * out_es : nullptr;
+    p.out_dtype = dtype;
+    p.cand = cand;
+    p.caph = L.caph;
+    p.T = T;
+    p.S = S;
+    p.k = k;
+    p.key_step = 1;
+    p.redo_count = redo;
+    p.redo_list = redo + 1;
+    p.tau_redo = tau_redo;
+    p.status = status_dev;
+    rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, p, idesc, grid, st);
+    if (rc != GW_OK) return rc;
+    if (sp.step > 0) {
+      // rows whose estimate was too high (normally none): same kernel, thresholds from tau_redo
+      IdxParams pr = p;
+      pr.tau_in = tau_redo;
+      pr.block_list = redo + 1;
+      pr.block_count = redo;
+      pr.redo_count = nullptr;
+      pr.redo_list = nullptr;
+      pr.tau_redo = nullptr;
+      rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, pr, idesc, grid, st);
+      if (rc != GW_OK) return rc;
+    }
+  }
+  return GW_OK;
+}

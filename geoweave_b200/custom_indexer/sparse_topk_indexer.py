@@ -1,0 +1,118 @@
+"""Indexer score + exact top-k -- same call signatures as the reference module
+``easyvolcap/utils/custom_indexer/sparse_topk_indexer.py`` (``sparse_topk_indexer_func`` :2188-2253) and the
+inference slot ``sparse_topk_indexer_inference_func`` the reference leaves open
+(``easyvolcap/utils/custom_indexer/__init__.py:4-7``, called at ``official_vggt/layers/indexer.py:570-581``).
+
+One fused tcgen05 kernel computes ``score[t,s] = sum_h w[s,h] * relu(scale * q[t,h].k[s,h])`` tile by tile and
+keeps the exact top-k per query in its epilogue; the score matrix is never written to memory.  The
+``block_k`` / ``merge_blocks`` / ``outer_query_chunk`` arguments tune the reference's block-wise loop and have no
+meaning here; they are accepted and ignored.  ``mask`` and ``view_bias_data`` are not implemented (both
+published presets run without them) and raise ``NotImplementedError`` -- there is no fallback path.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+__all__ = ["sparse_topk_indexer_func", "sparse_topk_indexer_inference_func", "indexer_scores", "clear_runtime_cache"]
+
+clear_runtime_cache = _lib.clear_runtime_cache
+
+
+def _check_qkw(q, k, w):
+    if q.dim() != 4 or k.dim() != 4 or w.dim() != 3:
+        raise ValueError(f"invalid shapes q={tuple(q.shape)} k={tuple(k.shape)} w={tuple(w.shape)}; "
+                         "expect q/k as [B,T(orS),H,D] and w as [B,S,H]")
+    bq, tq, hq, dq = q.shape
+    bk, sk, hk, dk = k.shape
+    bw, sw, hw = w.shape
+    if bq != bk or bq != bw or hq != hk or hq != hw or dq != dk or sk != sw:
+        raise ValueError("q/k/w shape mismatch")
+    if not (q.dtype == k.dtype == w.dtype):
+        raise TypeError("q/k/w must share one dtype")
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"the fused indexer takes bfloat16 or float16 inputs, got {q.dtype} "
+                        "(scores are always accumulated in fp32)")
+    return bq, tq, sk, hq, dq
+
+
+def fused_score_topk(q, k, w, topk: int, softmax_scale: Optional[float], return_scores: bool = True,
+                     out_indices: Optional[torch.Tensor] = None, out_scores: Optional[torch.Tensor] = None):
+    """q ``[B,T,Hi,Di]``, k ``[B,S,Hi,Di]``, w ``[B,S,Hi]`` -> (int32 ``[B,T,k]``, scores of q.dtype or None)."""
+    dev = _lib.require_cuda(q, k, w)
+    B, T, S, Hi, Di = _check_qkw(q, k, w)
+    q, k, w = q.contiguous(), k.contiguous(), w.contiguous()
+    topk = min(int(topk), S)
+    if topk <= 0:
+        raise ValueError("topk must be positive")
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(Di)
+    idx = out_indices if out_indices is not None else torch.empty((B, T, topk), device=dev, dtype=torch.int32)
+    sc = out_scores if out_scores is not None else (
+        torch.empty((B, T, topk), device=dev, dtype=q.dtype) if return_scores else None)
+    if idx.dtype != torch.int32 or tuple(idx.shape) != (B, T, topk) or not idx.is_contiguous():
+        raise ValueError(f"out_indices must be a contiguous int32 [B,T,{topk}] tensor")
+    if sc is not None and (sc.dtype != q.dtype or tuple(sc.shape) != (B, T, topk) or not sc.is_contiguous()):
+        raise ValueError(f"out_scores must be a contiguous {q.dtype} [B,T,{topk}] tensor")
+    if T == 0:
+        return idx, sc
+    lib = _lib.load()
+    nbytes = int(lib.gw_indexer_topk_workspace_bytes(B, T, S, Hi, Di, topk))
+    ws = _lib.workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        rc = lib.gw_indexer_topk_fused(q.data_ptr(), k.data_ptr(), w.data_ptr(), _lib.dtype_code(q), B, T, S, Hi, Di,
+                                       scale, topk, idx.data_ptr(), _lib.ptr(sc), ws.data_ptr(), ws.numel(),
+                                       _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "gw_indexer_topk_fused")
+    if _lib.debug_enabled():
+        _lib.check_status(dev)
+    return idx, sc
+
+
+def indexer_scores(q, k, w, softmax_scale: Optional[float] = None, key_step: int = 1) -> torch.Tensor:
+    """Dense fp32 scores ``[B,T,ceil(S/key_step)]`` from the same tensor-core main loop (verification and
+    threshold sampling; the counterpart of the reference's ``_compute_scores_block_einsum``, :935-951)."""
+    dev = _lib.require_cuda(q, k, w)
+    B, T, S, Hi, Di = _check_qkw(q, k, w)
+    q, k, w = q.contiguous(), k.contiguous(), w.contiguous()
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(Di)
+    m = (S + key_step - 1) // key_step
+    out = torch.empty((B, T, m), device=dev, dtype=torch.float32)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.gw_indexer_scores(q.data_ptr(), k.data_ptr(), w.data_ptr(), _lib.dtype_code(q), B, T, S, Hi, Di, scale,
+                                   int(key_step), out.data_ptr(), m, _lib.status_word(dev).data_ptr(),
+                                   _lib.stream_ptr(dev))
+    _lib.check(rc, "gw_indexer_scores")
+    if _lib.debug_enabled():
+        _lib.check_status(dev)
+    return out
+
+
+def _reject_mask(mask, view_bias_data):
+    if mask is not None and mask.numel() != 0:
+        raise NotImplementedError("an additive score mask is not implemented (presets run with sparse_use_mask=false)")
+    if view_bias_data is not None:
+        raise NotImplementedError("soft view bias is a training-time option and is not implemented")
+
+
+def sparse_topk_indexer_func(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, mask: Optional[torch.Tensor], topk: int,
+                             softmax_scale: Optional[float], block_k: int, merge_blocks: int = 0,
+                             view_bias_data: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(topk_indices int32 [B,T,k], topk_scores q.dtype [B,T,k])``; forward only."""
+    _reject_mask(mask, view_bias_data)
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or w.requires_grad):
+        q, k, w = q.detach(), k.detach(), w.detach()  # the reference computes the selection under no_grad (:2071)
+    with torch.no_grad():
+        return fused_score_topk(q, k, w, topk, softmax_scale, return_scores=True)
+
+
+@torch.inference_mode()
+def sparse_topk_indexer_inference_func(q, k, w, mask, topk, softmax_scale, topk_block=0, topk_merge_blocks=0,
+                                       outer_query_chunk: int = 0, return_scores: bool = True):
+    """Inference entry: ``(indices, scores | None)``."""
+    _reject_mask(mask, None)
+    return fused_score_topk(q, k, w, topk, softmax_scale, return_scores=return_scores)

@@ -1,0 +1,112 @@
+/*
+ * geoweave_b200 -- C ABI of the B200 (sm_100a) sparse top-k global-attention path.
+ *
+ * One shared library (libgeoweave_b200.so), plain pointers and sizes, no framework types.  Every pointer
+ * argument is a DEVICE pointer unless said otherwise; every call enqueues work on `stream` and returns
+ * without synchronising, allocates nothing and is safe to record into a CUDA graph (the exception is
+ * documented on the function).  Return value: GW_OK or a negative GW_ERR_* (see gw_strerror).  Conditions
+ * that can only be seen on the device (a bounded wait that ran out) are written to the caller's
+ * `status_dev` word, which the caller reads after its next synchronisation.
+ *
+ * Each entry point names the interface of the reference project (zss171999645/GeoWeave, paths relative to
+ * its root) that it replaces.
+ */
+#ifndef GEOWEAVE_B200_H
+#define GEOWEAVE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* gw_stream_t; /* a cudaStream_t */
+
+/* element types */
+#define GW_F32 0
+#define GW_BF16 1
+#define GW_F16 2
+
+/* status codes */
+#define GW_OK 0
+#define GW_ERR_INVALID_ARG (-1)  /* null pointer, non-positive size, misaligned pointer or stride */
+#define GW_ERR_UNSUPPORTED (-2)  /* a shape or dtype this build has no kernel for (there is no fallback) */
+#define GW_ERR_WORKSPACE (-3)    /* workspace smaller than gw_*_workspace_bytes() */
+#define GW_ERR_CUDA (-4)         /* a CUDA runtime/driver call failed; see gw_last_cuda_error() */
+#define GW_ERR_TIMEOUT (-5)      /* device side: a bounded wait inside a kernel ran out (status word) */
+#define GW_ERR_NO_SM100 (-6)     /* the current device is not compute capability 10.x */
+
+const char* gw_strerror(int code);
+int gw_last_cuda_error(void);   /* cudaError_t of the last GW_ERR_CUDA on this thread, else 0 */
+int gw_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Stage 1+2 fused: indexer score + exact top-k, the N x N score matrix never reaches memory.
+ *
+ *   score[t,s] = sum_h w[s,h] * relu(scale * <q_idx[t,h,:], k_idx[s,h,:]>)       (fp32)
+ *   out_idx[t,:] = the k keys with the largest score, equal scores keep the LOWER key index.
+ *
+ * q_idx [B,T,Hi,Di], k_idx [B,S,Hi,Di], w [B,S,Hi], contiguous, all of `dtype` (GW_BF16 or GW_F16).
+ * out_idx int32 [B,T,k] (order within a row unspecified), out_scores nullable, `dtype` [B,T,k].
+ * Requirements: Di == 64 (one 128-byte tensor-core K block per head), 1 <= Hi <= 8, k <= S.
+ * Replaces: easyvolcap/utils/custom_indexer/sparse_topk_indexer.py:2188 (sparse_topk_indexer_func),
+ *           :1241-1776 (_blockwise_topk_scores_impl), and the k=512-only fused kernel
+ *           easyvolcap/utils/custom_indexer/csrc/score_topk_fused_kernel.cu:52-224 (score_topk_fused_cuda).
+ * ---------------------------------------------------------------------------------------------- */
+size_t gw_indexer_topk_workspace_bytes(int B, int T, int S, int Hi, int Di, int k);
+int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
+                          int Hi, int Di, float scale, int k, int32_t* out_idx, void* out_scores,
+                          void* workspace, size_t workspace_bytes, int* status_dev, gw_stream_t stream);
+
+/* Dense score block (debug / verification / threshold sampling): out[t, j] = score[t, j*key_step] for
+ * j < ceil(S/key_step), fp32, row stride `out_row_stride` elements.  Same tensor-core main loop as the
+ * fused call.  Replaces: sparse_topk_indexer.py:935-951 (_compute_scores_block_einsum) and the Triton
+ * _score_block_kernel (:981-1062). */
+int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S, int Hi,
+                      int Di, float scale, int key_step, float* out, int64_t out_row_stride, int* status_dev,
+                      gw_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Stage 2 alone: exact top-k of materialised rows (any k <= cols; ties keep the lower column).
+ * scores [rows, cols] of `dtype` with row stride `row_stride` elements.  Either index output may be null:
+ * out_idx32 int32 [rows,k], out_idx64 int64 [rows,k]; out_scores nullable, `dtype` [rows,k].
+ * Rows are written in ascending column order.
+ * Replaces: easyvolcap/utils/custom_indexer/csrc/topk_exact_kernel.cu:25-149 (topk_exact_cuda, k = 512 only).
+ * ---------------------------------------------------------------------------------------------- */
+int gw_topk_exact(const void* scores, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int k,
+                  int32_t* out_idx32, int64_t* out_idx64, void* out_scores, gw_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Merge a running top-k list with a pending list: keep the best k of the union by (score descending,
+ * index ascending).  a_idx int32 [rows,ka]; b_pos int64 [rows,kb] with b_index = b_pos + b_start; negative
+ * indices are empty slots.  Scores of `dtype`.  Outputs [rows,k] (may alias the `a` arrays).
+ * Replaces: easyvolcap/utils/custom_indexer/csrc/merge_two_topk_kernel.cu:24-142 (merge_two_topk_cuda, k = 512 only).
+ * ---------------------------------------------------------------------------------------------- */
+int gw_merge_two_topk(const void* a_scores, const int32_t* a_idx, int ka, const void* b_scores,
+                      const int64_t* b_pos, int kb, int64_t b_start, int dtype, int64_t rows, int k,
+                      void* out_scores, int32_t* out_idx, gw_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Stage 3: attention of every query over only its selected keys (all heads of a query share one list).
+ *
+ *   out[t,h,:] = softmax_j(scale * <q[t,h,:], K[pos[t,j],h,:]>) . V[pos[t,j],h,:]
+ *
+ * q [B,T,H,D], k,v [B,S,H,D] given by element strides {batch, token, head} with a contiguous last
+ * dimension (so both the reference's [B,T,H,D] and [B,H,T,D] layouts are passed as they are);
+ * kv_pos int32 [B,T,K] contiguous, entries < 0 or >= S are padding.  out has strides out_strides and the
+ * same dtype; lse (nullable) fp32 [B,H,T] natural-log sum-exp; attn_sum (nullable) fp32 [B,T,K] = sum over
+ * heads of the softmax probabilities.  A row with only padding gives zeros and lse = -inf.
+ * Requirements: D in {32,64,128}; 16-byte aligned pointers; strides multiples of 16 bytes.
+ * Replaces: easyvolcap/utils/custom_flash_attn/sparse_index_flash_attn.py:122-259 (_fwd_kernel),
+ *           :375-458 (_attn_sum_kernel) and :2001-2233 (_flash_attn_forward).
+ * ---------------------------------------------------------------------------------------------- */
+int gw_sparse_attn_fwd(const void* q, const void* k, const void* v, const int32_t* kv_pos, int dtype, int B, int T,
+                       int S, int H, int D, int K, const int64_t q_strides[3], const int64_t k_strides[3],
+                       const int64_t v_strides[3], float scale, void* out, const int64_t out_strides[3], float* lse,
+                       float* attn_sum, int* status_dev, gw_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEOWEAVE_B200_H */

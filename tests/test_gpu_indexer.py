@@ -1,0 +1,163 @@
+"""GPU parity: tcgen05 indexer scores and the fused score + exact top-k, through the C ABI."""
+import pytest
+import torch
+
+import geoweave_b200
+from oracle import gw_oracle as orc
+from tests.gpu_util import dev, make_indexer_inputs, sorted_idx, t
+
+pytestmark = pytest.mark.gpu
+
+EXACT_CASES = ["idx_int", "idx_int_ties"]          # every partial sum exact in fp32: bit-exact whatever the order
+FLOAT_CASES = ["idx_bf16", "idx_bf16_ties", "idx_negw", "idx_kgeS"]
+
+
+def _inputs(c, dtype=torch.bfloat16):
+    return t(c["q_idx"], dtype), t(c["k_idx"], dtype), t(c["w"], dtype)
+
+
+@pytest.mark.parametrize("name", EXACT_CASES + FLOAT_CASES)
+def test_dense_scores_match_reference(golden, name):
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_scores
+
+    c = golden[name]
+    q, k, w = _inputs(c)
+    sc = indexer_scores(q, k, w, float(c["scale"]))
+    geoweave_b200.check_status()
+    ref = torch.from_numpy(c["scores"])
+    if name in EXACT_CASES:
+        assert torch.equal(sc.cpu(), ref)
+    else:
+        bound = 64 * 2.0**-24 * float(ref.abs().max()) * 8
+        assert (sc.cpu() - ref).abs().max().item() <= bound
+
+
+@pytest.mark.parametrize("step", [3, 7])
+def test_dense_scores_with_key_step(golden, step):
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_scores
+
+    c = golden["idx_int_ties"]
+    q, k, w = _inputs(c)
+    sc = indexer_scores(q, k, w, float(c["scale"]), key_step=step)
+    assert torch.equal(sc.cpu(), torch.from_numpy(c["scores"])[..., ::step])
+
+
+@pytest.mark.parametrize("name", EXACT_CASES)
+def test_fused_topk_bit_exact_on_exact_inputs(golden, name):
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    c = golden[name]
+    q, k, w = _inputs(c)
+    idx, sc = sparse_topk_indexer_func(q, k, w, q.new_empty(0), int(c["k"]), float(c["scale"]), 256)
+    geoweave_b200.check_status()
+    assert idx.dtype == torch.int32 and sc.dtype == q.dtype
+    assert torch.equal(sorted_idx(idx), torch.from_numpy(c["tie_idx"]).long())
+    ref_sc = torch.from_numpy(c["scores"]).gather(-1, idx.long().cpu())
+    assert torch.equal(sc.float().cpu(), ref_sc.bfloat16().float())
+
+
+@pytest.mark.parametrize("name", FLOAT_CASES)
+def test_fused_topk_on_float_inputs_audited(golden, name):
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_inference_func
+
+    c = golden[name]
+    q, k, w = _inputs(c)
+    kk = min(int(c["k"]), k.shape[1])
+    idx, none = sparse_topk_indexer_inference_func(q, k, w, None, int(c["k"]), float(c["scale"]), 256, 0, return_scores=False)
+    geoweave_b200.check_status()
+    assert none is None and idx.shape[-1] == kk
+    res = orc.audit_topk(idx, c["scores"], kk, c["q_idx"], c["k_idx"], c["w"], float(c["scale"]))
+    assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
+
+
+def test_same_scores_selection_is_bit_identical(golden):
+    """Scores made by the tensor-core kernel, selection by the fused epilogue vs the oracle on THOSE scores."""
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_scores
+
+    for seed, (T, S, k, ties) in enumerate([(300, 4164, 1024, False), (200, 5000, 64, True), (129, 1041, 512, True)]):
+        q, kx, w = [x.to(dev()) for x in make_indexer_inputs(T, S, seed=seed, ties=ties)]
+        dense = indexer_scores(q, kx, w, 0.125)
+        idx, sc = sparse_topk_indexer_func(q, kx, w, None, k, 0.125, 256)
+        geoweave_b200.check_status()
+        expect = orc.topk_tie_exact(dense.cpu(), k)
+        assert torch.equal(sorted_idx(idx), expect.long()), (T, S, k)
+
+
+@pytest.mark.parametrize("T,S,k,kind", [
+    (256, 8328, 256, "randn"),      # sampled threshold path (S >= 8k)
+    (256, 8328, 512, "ties"),
+    (200, 16656, 1024, "integer"),
+    (130, 33312, 1024, "randn"),
+    (130, 33312, 2048, "ties"),
+    (64, 4164, 1024, "randn"),      # streaming path (top 25 %)
+    (64, 2082, 2048, "integer"),
+])
+def test_fused_topk_at_scale(T, S, k, kind):
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    q, kx, w = make_indexer_inputs(T, S, seed=T + S + k, ties=(kind == "ties"), integer=(kind == "integer"))
+    idx, sc = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, k, 0.125, 256)
+    geoweave_b200.check_status()
+    scores = orc.indexer_scores(q, kx, w, 0.125)
+    if kind == "integer":
+        assert torch.equal(sorted_idx(idx), orc.topk_tie_exact(scores, k).long())
+    else:
+        res = orc.audit_topk(idx, scores, k, q, kx, w, 0.125)
+        assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
+        assert res["rows_equal"] >= 0.95 * res["rows"], res
+
+
+def test_adversarial_key_order_still_exact():
+    """Keys sorted so that scores rise with the index: the sampled threshold is useless and every list keeps
+    overflowing; the result must still be exact."""
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    T, S, k = 128, 8328, 256
+    g = torch.Generator().manual_seed(9)
+    q = torch.randint(0, 3, (1, T, 4, 64), generator=g).float()
+    kx = torch.randint(0, 3, (1, S, 4, 64), generator=g).float()
+    w = (torch.arange(S).float() // 16 / 1024).view(1, S, 1).expand(1, S, 4).contiguous()
+    q, kx, w = q.bfloat16(), kx.bfloat16(), w.bfloat16()
+    idx, _ = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, k, 0.125, 256)
+    geoweave_b200.check_status()
+    assert torch.equal(sorted_idx(idx), orc.topk_tie_exact(orc.indexer_scores(q, kx, w, 0.125), k).long())
+
+
+def test_all_equal_scores_pick_the_lowest_indices():
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    T, S, k = 70, 5000, 300
+    q = torch.zeros(1, T, 4, 64).bfloat16()
+    kx = torch.ones(1, S, 4, 64).bfloat16()
+    w = torch.ones(1, S, 4).bfloat16()
+    idx, sc = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, k, 0.125, 256)
+    geoweave_b200.check_status()
+    assert torch.equal(sorted_idx(idx), torch.arange(k).expand(1, T, k))
+    assert float(sc.abs().max()) == 0.0
+
+
+def test_fp16_inputs_and_fewer_heads():
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    for Hi in (1, 2, 3):
+        q, kx, w = make_indexer_inputs(100, 700, Hi=Hi, seed=Hi, dtype=torch.float16, integer=True)
+        idx, _ = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, 50, 0.125, 256)
+        geoweave_b200.check_status()
+        assert torch.equal(sorted_idx(idx), orc.topk_tie_exact(orc.indexer_scores(q, kx, w, 0.125), 50).long())
+
+
+def test_unsupported_arguments_fail_loudly():
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+    from geoweave_b200.custom_indexer.score_topk_fused_cuda import score_topk_fused_select
+
+    q, kx, w = [x.to(dev()) for x in make_indexer_inputs(10, 40, Hi=2, Di=32)]
+    with pytest.raises(geoweave_b200.GeoWeaveError):
+        sparse_topk_indexer_func(q, kx, w, None, 8, None, 0)  # head dim 32 has no kernel and no fallback
+    q, kx, w = [x.to(dev()) for x in make_indexer_inputs(10, 40)]
+    with pytest.raises(NotImplementedError):
+        sparse_topk_indexer_func(q, kx, w, torch.zeros(1, 10, 40, device=dev()), 8, None, 0)
+    with pytest.raises(TypeError):
+        sparse_topk_indexer_func(q.float(), kx.float(), w.float(), None, 8, None, 0)
+    sc, pos = score_topk_fused_select(q, kx, w, softmax_scale=0.125, out_pos=torch.empty(1, 10, 16, dtype=torch.int32, device=dev()))
+    assert pos.shape == (1, 10, 16) and sc.shape == (1, 10, 16)
