@@ -1,0 +1,315 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse top-k global-attention path (indexer score + exact top-k + sparse attention).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload vggt32|pi3_64|ctx256|small] [--impl ours|reference]
+
+One step = the path applied to every sparse global layer of the workload (VGGT 32 views: 11 layers of
+N = 33312 tokens, k = 1024, 16x64 attention heads, 4x64 indexer heads, bf16), each layer with its own
+synthetic ~N(0,1) inputs at the operator boundary.  With N > 1 GPUs the same global problem is split by
+query rows (strong scaling); per layer every rank all-gathers K, V, K_idx and w and nothing else.
+
+Prints ONE JSON line.  `value` = token-layer passes per second with inputs resident in HBM; `e2e` = the
+same through the public Python API with pinned-host inputs copied in and outputs copied out every step.
+`--impl reference` times the reference's CPU (`--backend torch`) op sequence on the host cores instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (views, tokens/view, layers, description)
+    "vggt32": (32, 1041, 11, "VGGT global layers 9-19, 32 views of 37x28 patches + 5 special tokens"),
+    "pi3_64": (64, 782, 9, "Pi3 sparse global layers 9-17, 64 views of 37x21 patches + 5 register tokens"),
+    "ctx256": (256, 1041, 1, "one VGGT-shaped layer over a 256-view context"),
+    "small": (4, 1041, 2, "4 views (reference's CPU-runnable size), 2 layers"),
+}
+H, D, HI, DI, TOPK = 16, 64, 4, 64, 1024
+METRIC = "global-attn tokens/s (indexer+top-k+sparse attn)"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="vggt32", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-rows", type=int, default=1024, help="query rows per CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers per step (profiling)")
+    ap.add_argument("--profile", action="store_true", help="profiling run: exact --warmup, no e2e pass, no CPU arm")
+    return ap.parse_args()
+
+
+def config_of(args, n_tokens, layers, desc, world):
+    return {"workload": f"{args.workload}: {desc}", "tokens": n_tokens, "layers_per_step": layers, "topk": TOPK,
+            "attn_heads": H, "head_dim": D, "indexer_heads": HI, "indexer_dim": DI,
+            "partition": f"query rows over {world} GPU(s); all-gather of K,V,K_idx,w per layer" if world > 1 else "single GPU",
+            "l2": "per-layer inputs (>= 230 MB for vggt32) exceed the 126 MB L2 and layers rotate; no explicit flush"}
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the reference's torch-backend op sequence on a bounded sample of query rows
+# ---------------------------------------------------------------------------------------------------
+def cpu_reference_tokens_per_s(n_tokens, rows, repeats, seed=7):
+    from oracle import gw_oracle as orc
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(seed)
+    q_idx = torch.randn(1, n_tokens, HI, DI, generator=g)
+    k_idx = torch.randn(1, n_tokens, HI, DI, generator=g)
+    w = torch.rand(1, n_tokens, HI, generator=g)
+    q = torch.randn(1, H, n_tokens, D, generator=g)
+    k = torch.randn(1, H, n_tokens, D, generator=g)
+    v = torch.randn(1, H, n_tokens, D, generator=g)
+    rows = min(rows, n_tokens)
+    times = []
+    with torch.no_grad():
+        for i in range(repeats + 1):
+            lo = (i * rows) % max(1, n_tokens - rows + 1)
+            t0 = time.perf_counter()
+            orc.reference_cpu_path(q_idx, k_idx, w, q, k, v, TOPK, DI ** -0.5, D ** -0.5, slice(lo, lo + rows))
+            times.append(time.perf_counter() - t0)
+    times = times[1:] if len(times) > 1 else times  # first call warms the allocator
+    per = statistics.median(times)
+    return rows / per, threads, per, f"{rows} query rows of one layer with all {n_tokens} keys resident, fp32, median of {len(times)}"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    views, tpv, layers, desc = WORKLOADS[args.workload]
+    n_tokens = views * tpv
+    t0 = time.perf_counter()
+    tps, threads, per, sample = cpu_reference_tokens_per_s(n_tokens, args.cpu_rows, max(1, args.steps))
+    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": n_tokens * layers / tps * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_of(args, n_tokens, layers, desc, 1),
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference is Python and is not present on the GPU box; this arm times a port of the op "
+                    "sequence its `--device cpu --backend torch` path executes (same ATen ops), all host threads; "
+                    "ms_per_step is extrapolated linearly in rows x layers",
+            "wall_s": time.perf_counter() - t0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks sampler
+# ---------------------------------------------------------------------------------------------------
+class Clocks:
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.samples = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append((time.perf_counter(), parts))
+
+    def stop(self, t_begin, t_end):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = [p for (t, p) in self.samples if t_begin <= t <= t_end] or [p for (_, p) in self.samples]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        pw = [float(r[2]) for r in rows if r[2].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(rows[0][1]) if rows[0][1].isdigit() else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(rows), "reasons": reasons}
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+
+    import geoweave_b200
+    from geoweave_b200 import _lib
+    from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_inference_func
+    from geoweave_b200.sharding import gather_rows, row_partition
+
+    _lib.load()  # fail loudly if the CUDA library is missing: there is no other path
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    views, tpv, layers, desc = WORKLOADS[args.workload]
+    if args.layers > 0:
+        layers = args.layers
+    n_tokens = views * tpv
+    lo, hi = row_partition(n_tokens, world)[rank]
+    rows = hi - lo
+    bf = torch.bfloat16
+
+    # per-layer inputs of this rank's token shard, on pinned host memory and resident on the device
+    host, resident = [], []
+    for layer in range(layers):
+        g = torch.Generator().manual_seed(1234 + 1000 * layer + rank)
+        t = {"q_idx": torch.randn(1, rows, HI, DI, generator=g).to(bf), "k_idx": torch.randn(1, rows, HI, DI, generator=g).to(bf),
+             "w": torch.rand(1, rows, HI, generator=g).to(bf), "q": torch.randn(1, rows, H, D, generator=g).to(bf),
+             "k": torch.randn(1, rows, H, D, generator=g).to(bf), "v": torch.randn(1, rows, H, D, generator=g).to(bf)}
+        t = {n: x.pin_memory() for n, x in t.items()}
+        host.append(t)
+        resident.append({n: x.to(dev) for n, x in t.items()})
+    out_host = [torch.empty((1, rows, H, D), dtype=bf).pin_memory() for _ in range(layers)]
+    staging = {n: torch.empty_like(x, device=dev) for n, x in host[0].items()}
+    h2d = sum(x.numel() * x.element_size() for t in host for x in t.values())
+    d2h = sum(x.numel() * x.element_size() for x in out_host)
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    stage_events = []  # (start, after indexer, after attention) per layer call, only while timing
+
+    def layer_op(t, record):
+        if world > 1:
+            k_idx, w, k, v = [gather_rows(t[n], n_tokens) for n in ("k_idx", "w", "k", "v")]
+        else:
+            k_idx, w, k, v = t["k_idx"], t["w"], t["k"], t["v"]
+        if record:
+            e0, e1, e2 = ev(), ev(), ev()
+            e0.record()
+        idx, _ = sparse_topk_indexer_inference_func(t["q_idx"], k_idx, w, None, TOPK, DI ** -0.5, 0, 0, return_scores=False)
+        if record:
+            e1.record()
+        out, _ = sparse_index_flash_attn_inference_func(t["q"], k, v, idx, None, False, D ** -0.5, False)
+        if record:
+            e2.record()
+            stage_events.append((e0, e1, e2))
+        return out
+
+    def step_resident(record=False):
+        for layer in range(layers):
+            layer_op(resident[layer], record)
+
+    def step_e2e():
+        for layer in range(layers):
+            for n, x in host[layer].items():
+                staging[n].copy_(x, non_blocking=True)
+            out = layer_op(staging, False)
+            out_host[layer].copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    n_warm = args.warmup if args.profile else max(3, args.warmup)
+    for _ in range(n_warm):
+        step_resident()
+    geoweave_b200.check_status()
+    clocks = Clocks(local) if rank == 0 else None
+    t_begin = time.perf_counter()
+    ms_total = timed(lambda: step_resident(True), args.steps)
+    t_end = time.perf_counter()
+    if args.profile:
+        ms_e2e = float("nan")
+    else:
+        step_e2e()
+        ms_e2e = timed(step_e2e, args.steps)
+    geoweave_b200.check_status()
+    clk = clocks.stop(t_begin, time.perf_counter()) if clocks else None
+
+    idx_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1, _ in stage_events)
+    att_ms = statistics.mean(e1.elapsed_time(e2) for _, e1, e2 in stage_events)
+    lib = _lib.load()
+    launches = layers * (lib.gw_indexer_topk_launch_count(1, rows, n_tokens, TOPK) + 1)
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        tc_peak = float(peaks.get("bf16_tflops", 1590.0))
+        peak_src = "measured (MEASURED_PEAKS.json)" if peaks else "fallback"
+        es = 2
+        attn_bytes = rows * (TOPK * 2 * H * D * es + TOPK * 4 + 2 * H * D * es)
+        attn_gbs = attn_bytes / (att_ms * 1e-3) / 1e9
+        idx_flops = 2.0 * rows * n_tokens * HI * DI
+        idx_tfs = idx_flops / (idx_ms * 1e-3) / 1e12
+        ms_step = ms_total / args.steps
+        value = n_tokens * layers / (ms_step * 1e-3)
+        e2e_value = n_tokens * layers / (ms_e2e / args.steps * 1e-3)
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
+                "ms_per_step": ms_step, "ms_per_layer": ms_step / layers, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_of(args, n_tokens, layers, desc, world),
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": ms_e2e / args.steps},
+                "gpu_launches": launches * args.steps,
+                "roofline": {"kernel": "sparse_attn_kernel (stage 3 gather)", "bound": "hbm", "achieved": attn_gbs, "peak": hbm_peak,
+                             "unit": "GB/s", "frac": attn_gbs / hbm_peak, "traffic": None, "peak_source": peak_src,
+                             "bytes_per_launch": attn_bytes, "ms_per_launch": att_ms},
+                "roofline_indexer": {"kernel": "indexer_kernel (stage 1+2, all launches of one call)", "bound": "tensor",
+                                     "achieved": idx_tfs, "peak": tc_peak, "unit": "TFLOP/s", "frac": idx_tfs / tc_peak,
+                                     "flops_per_call": idx_flops, "ms_per_call": idx_ms, "peak_source": peak_src},
+                "clocks": clk}
+        if world == 1 and not args.no_cpu_baseline and not args.profile:
+            tps, threads, per, sample = cpu_reference_tokens_per_s(n_tokens, args.cpu_rows, 2)
+            line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

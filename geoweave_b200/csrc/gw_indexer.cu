@@ -614,6 +614,12 @@ extern "C" size_t gw_indexer_topk_workspace_bytes(int B, int T, int S, int Hi, i
   return ws_layout(T, S, k).total;
 }
 
+extern "C" int gw_indexer_topk_launch_count(int B, int T, int S, int k) {
+  if (B <= 0 || T <= 0 || S <= 0 || k <= 0) return 0;
+  // w scaling + fused pass, plus sampled scores + threshold pick + redo pass when sampling is on
+  return B * (plan_sample(S, k).step > 0 ? 5 : 2);
+}
+
 extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
                                  int Hi, int Di, float scale, int key_step, float* out, int64_t out_row_stride,
                                  int* status_dev, gw_stream_t stream) {

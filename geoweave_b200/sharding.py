@@ -1,0 +1,91 @@
+"""Multi-GPU form of the path: query rows are split into contiguous slices, one per rank; every rank needs
+all keys, so K, V, K_idx and w are all-gathered once per layer (NCCL over NVLink) and nothing else is
+exchanged.  The reference has no multi-GPU form of this op; the split follows its own single-GPU
+query-chunk loop, which keeps K/V/K_idx resident and walks query chunks
+(easyvolcap/official_vggt/layers/dsa_attention.py:1138-1264, ``_run_sparse_streaming_direct``).
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+__all__ = ["row_partition", "shard_rows", "gather_rows", "sparse_global_attention_sharded"]
+
+
+def row_partition(n_rows: int, world_size: int) -> List[Tuple[int, int]]:
+    """Contiguous [start, stop) per rank; the first ``n_rows % world_size`` ranks get one extra row."""
+    if n_rows < 0 or world_size <= 0:
+        raise ValueError("n_rows must be >= 0 and world_size > 0")
+    base, extra = divmod(n_rows, world_size)
+    out, start = [], 0
+    for r in range(world_size):
+        size = base + (1 if r < extra else 0)
+        out.append((start, start + size))
+        start += size
+    return out
+
+
+def shard_rows(x: torch.Tensor, rank: int, world_size: int, dim: int = 1) -> torch.Tensor:
+    lo, hi = row_partition(x.shape[dim], world_size)[rank]
+    return x.narrow(dim, lo, hi - lo)
+
+
+def gather_rows(x: torch.Tensor, n_rows: int, group=None, dim: int = 1) -> torch.Tensor:
+    """All-gather row shards (``row_partition`` sizes along ``dim``) into the full ``n_rows`` tensor.
+
+    Equal shards go through one ``all_gather_into_tensor``; ragged shards are padded to the largest and
+    trimmed afterwards.  Every rank must call this with the same ``n_rows``; a shard whose size disagrees
+    with the partition raises before any communication.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    parts = row_partition(n_rows, world)
+    lo, hi = parts[rank]
+    if x.shape[dim] != hi - lo:
+        raise ValueError(f"rank {rank}: shard has {x.shape[dim]} rows, partition of {n_rows} over {world} expects {hi - lo}")
+    if world == 1:
+        return x
+    xm = x.movedim(dim, 0).contiguous()
+    biggest = max(b - a for a, b in parts)
+    if xm.shape[0] < biggest:
+        pad = torch.zeros((biggest - xm.shape[0],) + tuple(xm.shape[1:]), dtype=xm.dtype, device=xm.device)
+        xm = torch.cat([xm, pad], 0)
+    out = torch.empty((world * biggest,) + tuple(xm.shape[1:]), dtype=xm.dtype, device=xm.device)
+    if xm.is_cuda:
+        dist.all_gather_into_tensor(out, xm, group=group)
+    else:  # gloo (CPU tests)
+        chunks = list(out.chunk(world, 0))
+        dist.all_gather(chunks, xm, group=group)
+    if any(b - a != biggest for a, b in parts):
+        out = torch.cat([out[r * biggest: r * biggest + (b - a)] for r, (a, b) in enumerate(parts)], 0)
+    return out.movedim(0, dim)
+
+
+def sparse_global_attention_sharded(q_idx, k_idx, w, q, k, v, topk: int, n_tokens: int, group=None,
+                                    idx_scale=None, attn_scale=None, ops=None):
+    """One layer of the path on this rank's token shard (all tensors ``[B, rows_of_this_rank, ...]``).
+
+    Returns ``(out [B, rows, H, D], indices int32 [B, rows, k])`` for this rank's query rows; indices are
+    global key indices.  ``ops`` = (indexer, attention) callables, by default this library's CUDA ops (the
+    CPU tests pass stand-ins to exercise the bookkeeping without a GPU).
+    """
+    if ops is None:
+        from .custom_flash_attn import sparse_index_flash_attn_inference_func
+        from .custom_indexer import sparse_topk_indexer_inference_func
+
+        def indexer(qi, ki, ww, kk, sc):
+            return sparse_topk_indexer_inference_func(qi, ki, ww, None, kk, sc, 0, 0, return_scores=False)[0]
+
+        def attention(qq, kk_, vv, pos, sc):
+            return sparse_index_flash_attn_inference_func(qq, kk_, vv, pos, None, False, sc, False)[0]
+    else:
+        indexer, attention = ops
+    k_idx_full = gather_rows(k_idx, n_tokens, group)
+    w_full = gather_rows(w, n_tokens, group)
+    k_full = gather_rows(k, n_tokens, group)
+    v_full = gather_rows(v, n_tokens, group)
+    idx = indexer(q_idx, k_idx_full, w_full, topk, idx_scale)
+    out = attention(q, k_full, v_full, idx, attn_scale)
+    return out, idx

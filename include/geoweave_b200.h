@@ -49,7 +49,7 @@ int gw_abi_version(void);
  *
  * q_idx [B,T,Hi,Di], k_idx [B,S,Hi,Di], w [B,S,Hi], contiguous, all of `dtype` (GW_BF16 or GW_F16).
  * out_idx int32 [B,T,k] (order within a row unspecified), out_scores nullable, `dtype` [B,T,k].
- * Requirements: Di == 64 (one 128-byte tensor-core K block per head), 1 <= Hi <= 8, k <= S.
+ * Requirements: Di == 64 (one 128-byte tensor-core K block per head), 1 <= Hi <= 4, k <= S.
  * Replaces: easyvolcap/utils/custom_indexer/sparse_topk_indexer.py:2188 (sparse_topk_indexer_func),
  *           :1241-1776 (_blockwise_topk_scores_impl), and the k=512-only fused kernel
  *           easyvolcap/utils/custom_indexer/csrc/score_topk_fused_kernel.cu:52-224 (score_topk_fused_cuda).
@@ -58,6 +58,10 @@ size_t gw_indexer_topk_workspace_bytes(int B, int T, int S, int Hi, int Di, int 
 int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
                           int Hi, int Di, float scale, int k, int32_t* out_idx, void* out_scores,
                           void* workspace, size_t workspace_bytes, int* status_dev, gw_stream_t stream);
+
+/* Number of kernels one gw_indexer_topk_fused call enqueues (it depends on whether the key set is large
+ * enough for the sampled threshold pass).  Host-only arithmetic; no reference counterpart. */
+int gw_indexer_topk_launch_count(int B, int T, int S, int k);
 
 /* Dense score block (debug / verification / threshold sampling): out[t, j] = score[t, j*key_step] for
  * j < ceil(S/key_step), fp32, row stride `out_row_stride` elements.  Same tensor-core main loop as the
@@ -71,7 +75,7 @@ int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int d
  * Stage 2 alone: exact top-k of materialised rows (any k <= cols; ties keep the lower column).
  * scores [rows, cols] of `dtype` with row stride `row_stride` elements.  Either index output may be null:
  * out_idx32 int32 [rows,k], out_idx64 int64 [rows,k]; out_scores nullable, `dtype` [rows,k].
- * Rows are written in ascending column order.
+ * The order inside an output row is unspecified (the reference's torch.topk(sorted=False) leaves it open too).
  * Replaces: easyvolcap/utils/custom_indexer/csrc/topk_exact_kernel.cu:25-149 (topk_exact_cuda, k = 512 only).
  * ---------------------------------------------------------------------------------------------- */
 int gw_topk_exact(const void* scores, int dtype, int64_t rows, int64_t cols, int64_t row_stride, int k,

@@ -209,3 +209,31 @@ def audit_topk(idx_test, scores_oracle, k: int, q_idx=None, k_idx=None, w=None, 
         res["unexplained"] += int((gap > bound).sum())
         res["max_gap"] = max(res["max_gap"], float(gap.max()))
     return res
+
+
+def reference_cpu_path(q_idx, k_idx, w, q, k, v, topk: int, idx_scale: float, attn_scale: float, rows: slice):
+    """The op sequence the reference's ``--device cpu --backend torch`` path executes for a slice of query rows
+    (geoweave/inference.py:56-60): dense fp32 scores (indexer.py:452-455), ``torch.topk(sorted=False)``
+    (indexer.py:602), then gather / matmul / softmax / matmul (dsa_attention.py:4731-4753).  Used as the timed
+    CPU arm of the benchmark; query rows are independent, so a slice of rows with all keys resident costs
+    exactly its share of the full problem.  Layouts: q_idx ``[1,T,Hi,Di]``, q/k/v ``[1,H,N,D]`` (the
+    reference's), fp32."""
+    qi = q_idx[:, rows]
+    hs = torch.einsum("bthd,bshd->bths", qi, k_idx) * idx_scale
+    hs = torch.relu(hs)
+    hs = hs * w.permute(0, 2, 1).unsqueeze(1)
+    scores = hs.sum(dim=2, dtype=torch.float32)
+    idx = scores.topk(min(topk, scores.shape[-1]), dim=-1, sorted=False)[1]
+    B, H, S, D = k.shape
+    T = idx.shape[1]
+
+    def gather(x):
+        flat = idx[:, None].expand(B, H, T, idx.shape[2]).reshape(B * H, -1)
+        return x.reshape(B * H, S, D).gather(1, flat.unsqueeze(-1).expand(-1, -1, D)).reshape(B, H, T, -1, D)
+
+    k_sel = gather(k)
+    sc = torch.matmul(q[:, :, rows].unsqueeze(-2), k_sel.transpose(-1, -2)).squeeze(-2) * attn_scale
+    del k_sel
+    attn = sc.softmax(dim=-1)
+    out = torch.matmul(attn.unsqueeze(-2), gather(v)).squeeze(-2)
+    return out, idx
