@@ -23,6 +23,7 @@
 // result is exact whatever the data.
 #include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include "gw_common.cuh"
 #include "gw_select.cuh"
@@ -63,6 +64,7 @@ struct IdxParams {
   int* redo_list;
   float* tau_redo;         // [T] -inf for rows to redo, +inf for finished rows
   int* status;
+  int debug;               // timing experiments only (GW_IDX_DEBUG): 1 skip final select, 2 never append, 4 skip score math
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -289,6 +291,10 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           for (int h = 0; h < HI; ++h) tmem_ld_x16(taddr_row + h * BN + c0, a[h]);
           tmem_wait_ld();
           float sc[16];
+          if (p.debug & 4) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) sc[c] = __uint_as_float(a[0][c]);
+          } else
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
             const int col = col_base + c0 + c;
@@ -304,7 +310,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
               const int col = col_base + c0 + c;
-              if (sc[c] >= tau && col < p.S) {
+              if (sc[c] >= tau && col < p.S && !(p.debug & 2)) {
                 mybuf[cnt] = make_uint2(__float_as_uint(sc[c]), static_cast<uint32_t>(col));
                 ++cnt;
                 smin = fminf(smin, sc[c]);
@@ -367,7 +373,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int r = e; r < BM; r += EPI_WARPS) {
           const int n0 = sh->cnt[0][r], n1 = sh->cnt[1][r];
           const int grow = rb * BM + r;
-          if (n0 < 0 || grow >= p.T || sh->abort_flag) continue;
+          if (n0 < 0 || grow >= p.T || sh->abort_flag || (p.debug & 1)) continue;
           const int n = n0 + n1;
           if (n < p.k) {  // the sampled threshold was too high for this row: redo it from -inf
             if (lane == 0) {
@@ -745,6 +751,10 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     p.redo_list = redo + 1;
     p.tau_redo = tau_redo;
     p.status = status_dev;
+    {
+      const char* dbg = getenv("GW_IDX_DEBUG");
+      p.debug = dbg ? atoi(dbg) : 0;
+    }
     rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, p, idesc, grid, st);
     if (rc != GW_OK) return rc;
     if (sp.step > 0) {
