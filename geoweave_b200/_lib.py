@@ -42,6 +42,8 @@ SIGNATURES = {
                                       c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "gw_indexer_scores": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "gw_indexer_scores_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                          c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "gw_topk_exact": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "gw_merge_two_topk": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_int,
                                   c_void_p, c_void_p, c_void_p]),

@@ -772,3 +772,82 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
   }
   return GW_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// gw_indexer_scores without any allocation: the w*scale table lives in a fixed array of the library image
+// ---------------------------------------------------------------------------------------------
+namespace gw {
+namespace {
+
+static __device__ __align__(256) float4 g_noalloc_wsc[GW_NOALLOC_MAX_KEYS];  // 4 MiB per GPU that loads the library
+
+constexpr int kMaxDevices = 64;
+float4* g_noalloc_ptr[kMaxDevices] = {};  // device address of the array above, per device (host code cannot use the symbol itself)
+
+// Host code sees g_noalloc_wsc only as a stand-in symbol; the kernels need its device address, which differs per
+// device and is looked up once, with that device current.
+int noalloc_scratch(float4** out) {
+  int dev = 0;
+  GW_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return GW_ERR_UNSUPPORTED;
+  float4* ptr = __atomic_load_n(&g_noalloc_ptr[dev], __ATOMIC_ACQUIRE);
+  if (ptr == nullptr) {
+    void* addr = nullptr;
+    GW_CUDA_TRY(cudaGetSymbolAddress(&addr, g_noalloc_wsc));
+    ptr = static_cast<float4*>(addr);
+    __atomic_store_n(&g_noalloc_ptr[dev], ptr, __ATOMIC_RELEASE);  // racing first calls store the same value
+  }
+  *out = ptr;
+  return GW_OK;
+}
+
+}  // namespace
+}  // namespace gw
+
+extern "C" int gw_indexer_scores_noalloc(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T,
+                                         int S, int Hi, int Di, float scale, int key_step, float* out,
+                                         int64_t out_row_stride, int* status_dev, gw_stream_t stream) {
+  int rc = check_common(q_idx, k_idx, w, dtype, B, T, S, Hi, Di);
+  if (rc != GW_OK) return rc;
+  if (!out || key_step <= 0) return GW_ERR_INVALID_ARG;
+  const int m = (S + key_step - 1) / key_step;
+  if (out_row_stride < m) return GW_ERR_INVALID_ARG;
+  const int64_t s_pad = static_cast<int64_t>(round_up(static_cast<size_t>(S), BN)) + static_cast<int64_t>(BN) * key_step + BN;
+  if (s_pad > GW_NOALLOC_MAX_KEYS) return GW_ERR_TOO_LARGE;
+  if (T == 0) return GW_OK;
+  int sms = 0;
+  rc = device_info(&sms);
+  if (rc != GW_OK) return rc;
+  float4* wsc = nullptr;
+  rc = noalloc_scratch(&wsc);
+  if (rc != GW_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t row_bytes = static_cast<size_t>(Hi) * DI * 2;
+  const int nblocks = (T + BM - 1) / BM;
+  const int grid = nblocks < sms ? nblocks : sms;
+  for (int b = 0; b < B; ++b) {
+    const unsigned char* qb = static_cast<const unsigned char*>(q_idx) + static_cast<size_t>(b) * T * row_bytes;
+    const unsigned char* kb = static_cast<const unsigned char*>(k_idx) + static_cast<size_t>(b) * S * row_bytes;
+    const unsigned char* wb = static_cast<const unsigned char*>(w) + static_cast<size_t>(b) * S * Hi * 2;
+    // every table entry the score kernel reads (keys 0 .. s_pad-1, zero beyond S) is rewritten here first
+    rc = launch_prep_w(wb, dtype, S, Hi, scale, wsc, static_cast<int>(s_pad), st);
+    if (rc != GW_OK) return rc;
+    CUtensorMap mq, mk;
+    rc = make_map(&mq, qb, dtype, T, Hi, row_bytes, BM);
+    if (rc != GW_OK) return rc;
+    rc = make_map(&mk, kb, dtype, m, Hi, row_bytes * key_step, BN);
+    if (rc != GW_OK) return rc;
+    IdxParams p{};
+    p.wsc = wsc;
+    p.dense_out = out + static_cast<int64_t>(b) * T * out_row_stride;
+    p.dense_stride = out_row_stride;
+    p.T = T;
+    p.S = m;
+    p.k = 0;
+    p.key_step = key_step;
+    p.status = status_dev;
+    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc(dtype == GW_BF16 ? 1 : 0), grid, st);
+    if (rc != GW_OK) return rc;
+  }
+  return GW_OK;
+}

@@ -220,6 +220,7 @@ extern "C" const char* gw_strerror(int code) {
     case GW_ERR_CUDA: return "CUDA call failed (see gw_last_cuda_error)";
     case GW_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
     case GW_ERR_NO_SM100: return "device is not compute capability 10.x";
+    case GW_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of a no-allocation entry point";
     default: return "unknown geoweave_b200 status";
   }
 }

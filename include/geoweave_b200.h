@@ -36,6 +36,7 @@ typedef struct CUstream_st* gw_stream_t; /* a cudaStream_t */
 #define GW_ERR_CUDA (-4)         /* a CUDA runtime/driver call failed; see gw_last_cuda_error() */
 #define GW_ERR_TIMEOUT (-5)      /* device side: a bounded wait inside a kernel ran out (status word) */
 #define GW_ERR_NO_SM100 (-6)     /* the current device is not compute capability 10.x */
+#define GW_ERR_TOO_LARGE (-7)    /* the problem exceeds the fixed capacity of a no-allocation entry point */
 
 const char* gw_strerror(int code);
 int gw_last_cuda_error(void);   /* cudaError_t of the last GW_ERR_CUDA on this thread, else 0 */
@@ -70,6 +71,25 @@ int gw_indexer_topk_launch_count(int B, int T, int S, int k);
 int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S, int Hi,
                       int Di, float scale, int key_step, float* out, int64_t out_row_stride, int* status_dev,
                       gw_stream_t stream);
+
+/* gw_indexer_scores for callers that must not allocate.  No counterpart in the reference.
+ *
+ * gw_indexer_scores needs a scratch table (w * scale as fp32, 16 bytes per key) and gets it from the stream-
+ * ordered allocator.  Some hosts cannot do that: a plugin loaded into a serving runtime that owns the whole
+ * device heap and forbids plugin-side allocation, or a latency-critical loop that cannot accept the
+ * device-wide synchronisation an allocation may imply.  This variant keeps the table in a fixed 4 MiB array
+ * that is part of the library image (every GPU that loads the library holds these 4 MiB until the process
+ * exits) and calls no allocating routine.  Same arguments, same results.
+ *
+ * Limit: round_up(S, 64) + 64 * key_step + 64 <= GW_NOALLOC_MAX_KEYS, otherwise GW_ERR_TOO_LARGE and nothing
+ * is launched.  The first call on each device looks up the array's device address (with that device
+ * current); make that first call before any stream capture.  All calls on a device share the one array:
+ * each call rewrites every entry it reads, so stale contents never matter, but two calls whose kernels may
+ * overlap on the GPU (different streams) race on it -- serialise them. */
+#define GW_NOALLOC_MAX_KEYS 262144
+int gw_indexer_scores_noalloc(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
+                              int Hi, int Di, float scale, int key_step, float* out, int64_t out_row_stride,
+                              int* status_dev, gw_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Stage 2 alone: exact top-k of materialised rows (any k <= cols; ties keep the lower column).
