@@ -37,6 +37,7 @@ SIGNATURES = {
     "gw_last_cuda_error": (c_int, []),
     "gw_abi_version": (c_int, []),
     "gw_indexer_topk_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    "gw_debug_indexer_profile": (c_int, [c_void_p, c_int]),
     "gw_indexer_topk_launch_count": (c_int, [c_int, c_int, c_int, c_int]),
     "gw_indexer_topk_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                       c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),

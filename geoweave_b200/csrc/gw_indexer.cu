@@ -27,6 +27,7 @@
 
 #include "gw_common.cuh"
 #include "gw_select.cuh"
+#include "gw_tc.cuh"
 
 namespace gw {
 namespace {
@@ -58,70 +59,15 @@ struct IdxParams {
   int caph;
   int T, S, k;
   int key_step;            // score mode: column j is key j * key_step
-  const int* block_list;   // redo launch: row blocks to process ...
-  const int* block_count;  // ... and how many; null = all blocks
-  int* redo_count;         // first launch: rows that ended short are reported here
-  int* redo_list;
-  float* tau_redo;         // [T] -inf for rows to redo, +inf for finished rows
+  const float* smax_in;    // [T] fast path: estimate of the row maximum (binning range of the final selection)
+  int row_begin, row_end;  // fast path: rows of this launch (row_begin a multiple of the row block)
+  int* list_cnt;           // fast path: [rows of the launch][2] list lengths (caph + 1 = overflowed)
+  int* block_flags;        // [row blocks] fast kernel: sets 1 for blocks with a row to redo; robust kernel, when
+                           // non-null: processes only the flagged blocks
+  float* tau_redo;         // [T] fast kernel output: -inf for rows to redo, +inf for finished rows
   int* status;
-  int debug;               // timing experiments only (GW_IDX_DEBUG): 1 skip final select, 2 never append, 4 skip score math
+  int debug;               // timing experiments only (GW_IDX_DEBUG): 1 skip final select, 2 never append, 4 skip score math, 8 skip TMEM reads, 16 skip MMA
 };
-
-// ---------------------------------------------------------------------------------------------
-// tcgen05 / TMA wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-          smem_u32(dst)),
-      "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major operand tile, rows of 128 bytes, 128-byte swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);        // start address
-  d |= static_cast<uint64_t>(1) << 16;                         // leading byte offset (unused with swizzle)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;                 // stride byte offset
-  d |= static_cast<uint64_t>(1) << 46;                         // descriptor version (sm_100)
-  d |= static_cast<uint64_t>(2) << 61;                         // 128-byte swizzle
-  return d;
-}
-// kind::f16 instruction descriptor: fp32 accumulate, A and B K-major, M=128, N=64
-__host__ __device__ constexpr uint32_t make_idesc(int ab_format) {
-  return (1u << 4) | (static_cast<uint32_t>(ab_format) << 7) | (static_cast<uint32_t>(ab_format) << 10) |
-         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
-}
 
 struct TwoSegSrc {
   const uint2* a;
@@ -159,7 +105,6 @@ struct alignas(8) IdxShared {
   uint64_t acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
-  int block_failed;
   int cnt[2][BM];
   float smin[2][BM];
   float smax[2][BM];
@@ -178,8 +123,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   IdxShared* sh = reinterpret_cast<IdxShared*>(sel + EPI_WARPS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nblocks_all = (p.T + BM - 1) / BM;
-  const int nwork = (p.block_count != nullptr) ? *p.block_count : nblocks_all;
+  const int nwork = (p.T + BM - 1) / BM;
   const int ntiles = (p.S + BN - 1) / BN;
 
   if (threadIdx.x == 0) {
@@ -194,7 +138,6 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(&sh->acc_empty[b], 4);
     }
     sh->abort_flag = 0;
-    sh->block_failed = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
   }
@@ -208,9 +151,11 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t kuse = 0, nblk = 0;
-      for (int wi = blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x, ++nblk) {
-        const int rb = p.block_list ? p.block_list[wi] : wi;
+      for (int wi = blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x) {
+        if (p.block_flags && !p.block_flags[wi]) continue;
+        const int rb = wi;
         if (!mbar_wait_bounded(&sh->q_empty, (nblk & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+        ++nblk;
         mbar_arrive_expect_tx(&sh->q_full, HI * Q_HEAD_BYTES);
 #pragma unroll
         for (int h = 0; h < HI; ++h) tma_load_2d(q_smem + h * Q_HEAD_BYTES, &tmQ, h * DI, rb * BM, &sh->q_full);
@@ -230,8 +175,10 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       uint32_t kuse = 0, nblk = 0, use0 = 0, use1 = 0;
-      for (int wi = blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x, ++nblk) {
+      for (int wi = blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x) {
+        if (p.block_flags && !p.block_flags[wi]) continue;
         if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
+        ++nblk;
         for (int j = 0; j < ntiles; ++j, ++kuse) {
           const uint32_t b = j & 1;
           const uint32_t n = b ? use1 : use0;
@@ -241,7 +188,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (sh->abort_flag) break;
           tc_fence_after();
 #pragma unroll
-          for (int h = 0; h < HI; ++h) {
+          for (int h = 0; h < HI && !(p.debug & 16); ++h) {
             const uint64_t adesc = make_smem_desc(smem_u32(q_smem + h * Q_HEAD_BYTES));
             const uint64_t bdesc = make_smem_desc(smem_u32(k_smem + (s * HI + h) * K_HEAD_BYTES));
             const uint32_t d = tmem_base + b * ACC_COLS + h * BN;
@@ -271,7 +218,8 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int compact_at = p.caph - BN;
 
     for (int wi = blockIdx.x; wi < nwork; wi += gridDim.x) {
-      const int rb = p.block_list ? p.block_list[wi] : wi;
+      if (p.block_flags && !p.block_flags[wi]) continue;
+      const int rb = wi;
       const int row = rb * BM + row_in_tile;
       float tau = INFINITY;
       if (row < p.T) tau = p.tau_in ? p.tau_in[row] : -INFINITY;
@@ -286,6 +234,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int col_base = j * BN;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (p.debug & 8) break;
           uint32_t a[HI][16];
 #pragma unroll
           for (int h = 0; h < HI; ++h) tmem_ld_x16(taddr_row + h * BN + c0, a[h]);
@@ -375,14 +324,6 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const int grow = rb * BM + r;
           if (n0 < 0 || grow >= p.T || sh->abort_flag || (p.debug & 1)) continue;
           const int n = n0 + n1;
-          if (n < p.k) {  // the sampled threshold was too high for this row: redo it from -inf
-            if (lane == 0) {
-              sh->block_failed = 1;
-              if (p.tau_redo) p.tau_redo[grow] = -INFINITY;
-            }
-            continue;
-          }
-          if (lane == 0 && p.tau_redo) p.tau_redo[grow] = INFINITY;
           const uint2* b0 = p.cand + ((static_cast<size_t>(blockIdx.x) * BM + r) * 2 + 0) * p.caph;
           const uint2* b1 = b0 + p.caph;
           const float lo_s = fminf(sh->smin[0][r], sh->smin[1][r]);
@@ -397,13 +338,6 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                           composite(score_key(hi_s), 0u), sel[e], lane, 0, sink, nullptr);
         }
         named_bar_sync(1, EPI_WARPS * 32);
-        if (e == 0 && lane == 0 && sh->block_failed) {
-          sh->block_failed = 0;
-          if (p.redo_count) {
-            const int pos = atomicAdd(p.redo_count, 1);
-            p.redo_list[pos] = rb;
-          }
-        }
       }
       if (sh->abort_flag) break;
     }
@@ -415,6 +349,12 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
+
+}  // namespace
+}  // namespace gw
+#include "gw_indexer_fast.cuh"
+namespace gw {
+namespace {
 
 // w * scale as fp32, four per key; rows beyond S (tile padding) are zero
 template <typename T>
@@ -439,7 +379,7 @@ struct NullSink {
 };
 constexpr int KTH_WARPS = 8;
 __global__ void __launch_bounds__(KTH_WARPS * 32) kth_rows_kernel(const float* sc, int m, int64_t stride, int T, int r,
-                                                                  float* tau) {
+                                                                  float* tau, float* smax) {
   __shared__ SelectSmem<SEL_BINS> sm[KTH_WARPS];
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * KTH_WARPS + w;
@@ -460,7 +400,10 @@ __global__ void __launch_bounds__(KTH_WARPS * 32) kth_rows_kernel(const float* s
   group_select_topk<32, SEL_BINS>(src, m, r, static_cast<unsigned long long>(kmin) << 32,
                                   (static_cast<unsigned long long>(kmax) << 32) | 0xffffffffull, sm[w], lane, 0,
                                   NullSink{}, &kth);
-  if (lane == 0) tau[row] = key_score(composite_key(kth));
+  if (lane == 0) {
+    tau[row] = key_score(composite_key(kth));
+    smax[row] = key_score(kmax);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -534,6 +477,28 @@ int launch_indexer(int Hi, const CUtensorMap& mq, const CUtensorMap& mk, const I
   return GW_OK;
 }
 
+int launch_indexer_fast(int Hi, const CUtensorMap& mq, const CUtensorMap& mk, const IdxParams& p, uint32_t idesc, int grid,
+                        cudaStream_t st) {
+  const size_t smem = fast_smem_bytes(Hi);
+#define GW_IDXF_CASE(H)                                                                                         \
+  case H: {                                                                                                     \
+    auto kern = indexer_fast_kernel<H>;                                                                         \
+    GW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))); \
+    kern<<<grid, F_THREADS, smem, st>>>(mq, mk, p, idesc);                                                      \
+    break;                                                                                                      \
+  }
+  switch (Hi) {
+    GW_IDXF_CASE(1)
+    GW_IDXF_CASE(2)
+    GW_IDXF_CASE(3)
+    GW_IDXF_CASE(4)
+    default: return GW_ERR_UNSUPPORTED;
+  }
+#undef GW_IDXF_CASE
+  GW_LAUNCH_CHECK();
+  return GW_OK;
+}
+
 int launch_prep_w(const void* w, int dtype, int S, int Hi, float scale, float4* wsc, int s_pad, cudaStream_t st) {
   const int thr = 256, grid = (s_pad + thr - 1) / thr;
   if (dtype == GW_BF16)
@@ -573,8 +538,8 @@ int cand_capacity(int k) {
 }
 
 struct WsLayout {
-  size_t wsc, tau0, tau_redo, redo, sample, cand, total;
-  int s_pad, m_pad, slots, caph;
+  size_t wsc, tau0, smax, tau_redo, flags, sample, list_cnt, cand, total;
+  int s_pad, m_pad, slots, caph, chunk_rows;
 };
 WsLayout ws_layout(int T, int S, int k) {
   WsLayout L;
@@ -593,10 +558,20 @@ WsLayout ws_layout(int T, int S, int k) {
   };
   L.wsc = take(static_cast<size_t>(L.s_pad) * 16);
   L.tau0 = take(static_cast<size_t>(T) * 4);
+  L.smax = take(static_cast<size_t>(T) * 4);
   L.tau_redo = take(static_cast<size_t>(T) * 4);
-  L.redo = take(static_cast<size_t>(nblocks + 1) * 4);
+  L.flags = take(static_cast<size_t>(nblocks) * 4);
   L.sample = take(static_cast<size_t>(T) * L.m_pad * 4);
-  L.cand = take(static_cast<size_t>(L.slots) * BM * 2 * L.caph * 8);
+  // fast path: the lists of all rows of a launch are kept until the finalize kernel has run, so long inputs are
+  // processed in chunks of whole waves of row blocks (about 2 GiB of lists per chunk)
+  const size_t row_bytes = static_cast<size_t>(2) * L.caph * 8;
+  int chunk_blocks = static_cast<int>((static_cast<size_t>(2) << 30) / row_bytes / BM);
+  chunk_blocks = chunk_blocks >= 2 * MAX_SLOTS ? chunk_blocks / 148 * 148 : (chunk_blocks > 0 ? chunk_blocks : 1);
+  if (chunk_blocks > nblocks) chunk_blocks = nblocks;
+  L.chunk_rows = sp.step > 0 ? chunk_blocks * BM : 0;
+  L.list_cnt = take(static_cast<size_t>(L.chunk_rows) * 2 * 4);
+  const size_t robust_rows = static_cast<size_t>(L.slots) * BM;
+  L.cand = take((robust_rows > static_cast<size_t>(L.chunk_rows) ? robust_rows : static_cast<size_t>(L.chunk_rows)) * row_bytes);
   L.total = off;
   return L;
 }
@@ -620,10 +595,21 @@ extern "C" size_t gw_indexer_topk_workspace_bytes(int B, int T, int S, int Hi, i
   return ws_layout(T, S, k).total;
 }
 
+extern "C" int gw_debug_indexer_profile(unsigned long long* host_out, int max_entries) {
+  const int total = MAX_SLOTS * (F_THREADS / 32) * PROF_SLOTS;  // [CTA][10 warps][8 slots]
+  const int n = max_entries < total ? max_entries : total;
+  if (!host_out || n <= 0) return GW_ERR_INVALID_ARG;
+  GW_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_idx_prof, sizeof(unsigned long long) * n));
+  return n;
+}
+
 extern "C" int gw_indexer_topk_launch_count(int B, int T, int S, int k) {
   if (B <= 0 || T <= 0 || S <= 0 || k <= 0) return 0;
   // w scaling + fused pass, plus sampled scores + threshold pick + redo pass when sampling is on
-  return B * (plan_sample(S, k).step > 0 ? 5 : 2);
+  const WsLayout L = ws_layout(T, S, k);
+  if (L.chunk_rows == 0) return B * 2;
+  const int chunks = (T + L.chunk_rows - 1) / L.chunk_rows;
+  return B * (4 + 2 * chunks);  // w scaling, sampled scores, thresholds, redo pass + (filter, finalize) per chunk
 }
 
 extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
@@ -666,7 +652,7 @@ extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const voi
     p.k = 0;
     p.key_step = key_step;
     p.status = status_dev;
-    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc(dtype == GW_BF16 ? 1 : 0), grid, st);
+    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, BN), grid, st);
   }
   const cudaError_t fe = cudaFreeAsync(wsc, st);
   if (rc == GW_OK && fe != cudaSuccess) return cuda_fail(fe);
@@ -691,7 +677,9 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
   float4* wsc = reinterpret_cast<float4*>(ws + L.wsc);
   float* tau0 = reinterpret_cast<float*>(ws + L.tau0);
   float* tau_redo = reinterpret_cast<float*>(ws + L.tau_redo);
-  int* redo = reinterpret_cast<int*>(ws + L.redo);
+  float* smax = reinterpret_cast<float*>(ws + L.smax);
+  int* flags = reinterpret_cast<int*>(ws + L.flags);
+  int* list_cnt = reinterpret_cast<int*>(ws + L.list_cnt);
   float* sample = reinterpret_cast<float*>(ws + L.sample);
   uint2* cand = reinterpret_cast<uint2*>(ws + L.cand);
 
@@ -700,7 +688,7 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
   const int nblocks = (T + BM - 1) / BM;
   int grid = nblocks < sms ? nblocks : sms;
   if (grid > L.slots) grid = L.slots;
-  const uint32_t idesc = make_idesc(dtype == GW_BF16 ? 1 : 0);
+  const uint32_t idesc = make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, BN);
   const size_t out_es = dtype_size(dtype);
 
   for (int b = 0; b < B; ++b) {
@@ -728,16 +716,14 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
       ps.status = status_dev;
       rc = launch_indexer<MODE_SCORES>(Hi, mq, ms, ps, idesc, grid, st);
       if (rc != GW_OK) return rc;
-      kth_rows_kernel<<<(T + KTH_WARPS - 1) / KTH_WARPS, KTH_WARPS * 32, 0, st>>>(sample, sp.m, L.m_pad, T, sp.rank, tau0);
+      sample_threshold_kernel<<<(T + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(sample, sp.m, L.m_pad, T, sp.rank, tau0, smax);
       GW_LAUNCH_CHECK();
     }
 
     rc = make_map(&mk, kb, dtype, S, Hi, row_bytes, BN);
     if (rc != GW_OK) return rc;
-    GW_CUDA_TRY(cudaMemsetAsync(redo, 0, 4, st));
     IdxParams p{};
     p.wsc = wsc;
-    p.tau_in = sp.step > 0 ? tau0 : nullptr;
     p.out_idx = out_idx + static_cast<int64_t>(b) * T * k;
     p.out_scores = out_scores ? static_cast<unsigned char*>(out_scores) + static_cast<size_t>(b) * T * k * out_es : nullptr;
     p.out_dtype = dtype;
@@ -747,28 +733,41 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     p.S = S;
     p.k = k;
     p.key_step = 1;
-    p.redo_count = redo;
-    p.redo_list = redo + 1;
-    p.tau_redo = tau_redo;
     p.status = status_dev;
     {
       const char* dbg = getenv("GW_IDX_DEBUG");
       p.debug = dbg ? atoi(dbg) : 0;
     }
-    rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, p, idesc, grid, st);
-    if (rc != GW_OK) return rc;
-    if (sp.step > 0) {
-      // rows whose estimate was too high (normally none): same kernel, thresholds from tau_redo
-      IdxParams pr = p;
-      pr.tau_in = tau_redo;
-      pr.block_list = redo + 1;
-      pr.block_count = redo;
-      pr.redo_count = nullptr;
-      pr.redo_list = nullptr;
-      pr.tau_redo = nullptr;
-      rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, pr, idesc, grid, st);
+    if (sp.step == 0) {
+      // small key sets: the streaming kernel from tau = -inf
+      rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, p, idesc, grid, st);
       if (rc != GW_OK) return rc;
+      continue;
     }
+    GW_CUDA_TRY(cudaMemsetAsync(flags, 0, static_cast<size_t>(nblocks) * 4, st));
+    p.tau_in = tau0;
+    p.smax_in = smax;
+    p.tau_redo = tau_redo;
+    p.block_flags = flags;
+    p.list_cnt = list_cnt;
+    for (int r0 = 0; r0 < T; r0 += L.chunk_rows) {
+      p.row_begin = r0;
+      p.row_end = r0 + L.chunk_rows < T ? r0 + L.chunk_rows : T;
+      const int cblocks = (p.row_end - p.row_begin + BM - 1) / BM;
+      rc = launch_indexer_fast(Hi, mq, mk, p, idesc, cblocks < sms ? cblocks : sms, st);
+      if (rc != GW_OK) return rc;
+      finalize_lists_kernel<<<(p.row_end - p.row_begin + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(p);
+      GW_LAUNCH_CHECK();
+    }
+    // blocks with a row whose lists overflowed or came up short (normally none): streaming kernel from -inf
+    IdxParams pr = p;
+    pr.tau_in = tau_redo;
+    pr.smax_in = nullptr;
+    pr.tau_redo = nullptr;
+    pr.list_cnt = nullptr;
+    pr.debug = 0;
+    rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, pr, idesc, grid, st);
+    if (rc != GW_OK) return rc;
   }
   return GW_OK;
 }
@@ -846,7 +845,7 @@ extern "C" int gw_indexer_scores_noalloc(const void* q_idx, const void* k_idx, c
     p.k = 0;
     p.key_step = key_step;
     p.status = status_dev;
-    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc(dtype == GW_BF16 ? 1 : 0), grid, st);
+    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, BN), grid, st);
     if (rc != GW_OK) return rc;
   }
   return GW_OK;

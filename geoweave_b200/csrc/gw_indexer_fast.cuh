@@ -1,0 +1,405 @@
+// Fast form of the fused indexer for large key sets, where a sampled per-row threshold tau is available.
+// (Included by gw_indexer.cu after IdxParams, the candidate sources/sinks and the tile constants.)
+//
+// Same tensor-core main loop as indexer_kernel, but the epilogue only filters: a thread appends (score, key)
+// to its row's list in global memory when score >= tau, through predicated stores and a moving pointer (no
+// divergent branch, no selection inside the kernel).  TMEM reads are software-pipelined (the next 8 columns
+// are in flight while 8 are reduced) and the w*scale tile comes from a small shared-memory ring that the TMA
+// producer fills alongside the keys.  The lists of all rows of a launch stay in the workspace and a second,
+// occupancy-bound kernel (finalize_lists_kernel, one warp per row) turns each into the exact top-k.
+// A row whose list overflowed or holds fewer than k candidates is not resolved there: its row block is
+// flagged and the robust kernel redoes that block from tau = -inf.  The result is therefore exact for any
+// data; only the speed depends on the quality of tau.
+#pragma once
+
+#include "gw_select_tight.cuh"
+
+namespace gw {
+namespace {
+
+constexpr int F_EPI = 8;                        // epilogue warps (2 streams x 4 lane quarters)
+constexpr int F_THREADS = 64 + F_EPI * 32;      // 320
+constexpr int WSLOTS = 8;                       // w*scale tile ring
+constexpr int W_TILE_BYTES = BN * 16;
+
+// Cycle counters for performance diagnosis (filled when bit 32 of IdxParams::debug is set, read back with
+// gw_debug_indexer_profile): per CTA, per warp, eight 64-bit slots.
+constexpr int PROF_SLOTS = 8;
+__device__ unsigned long long g_idx_prof[MAX_SLOTS * (F_THREADS / 32) * PROF_SLOTS];  // [CTA][warp][slot]
+
+struct ProfClock {
+  unsigned long long acc[PROF_SLOTS] = {};
+  long long t0 = 0;
+  bool on;
+  __device__ explicit ProfClock(bool enabled) : on(enabled) {}
+  __device__ __forceinline__ void start() { if (on) t0 = clock64(); }
+  __device__ __forceinline__ void stop(int slot) { if (on) { const long long t1 = clock64(); acc[slot] += t1 - t0; t0 = t1; } }
+  __device__ void flush(int warp) const {
+    if (!on) return;
+    for (int i = 0; i < PROF_SLOTS; ++i) g_idx_prof[(blockIdx.x * (F_THREADS / 32) + warp) * PROF_SLOTS + i] = acc[i];
+  }
+};
+
+struct alignas(8) FastShared {
+  uint64_t q_full, q_empty;
+  uint64_t k_full[NSTG], k_empty[NSTG];
+  uint64_t acc_full[2], acc_empty[2];
+  uint64_t w_full[WSLOTS], w_empty[WSLOTS];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+#ifdef GW_FAST_NO_APPEND
+constexpr bool kFastNoAppend = true;
+#else
+constexpr bool kFastNoAppend = false;
+#endif
+
+template <int HI>
+__device__ __forceinline__ void fast_load_chunk(uint32_t taddr, uint32_t (&a)[HI][8]) {
+#pragma unroll
+  for (int h = 0; h < HI; ++h) tmem_ld_x8(taddr + h * BN, a[h]);
+}
+
+// store (bits, col) at *ptr when flag is set; a predicated store, never a branch
+__device__ __forceinline__ void store_if(uint2* ptr, uint32_t flag, uint32_t bits, uint32_t col) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %0, 0;\n\t"
+      "@p st.global.v2.u32 [%1], {%2, %3};\n\t}" ::"r"(flag),
+      "l"(ptr), "r"(bits), "r"(col)
+      : "memory");
+}
+
+// reduce 8 columns held in `a`, append the ones that pass.  All loads and all arithmetic come first; the
+// appends are predicated stores through a moving pointer, so the code has no divergent branch.  The caller
+// guarantees room for 8 more entries.
+template <int HI, bool GUARD>
+__device__ __forceinline__ void fast_reduce_chunk(const uint32_t (&a)[HI][8], const float4* __restrict__ wt, int col0, int S,
+                                                  float tau, uint2*& wp) {
+  float4 w4[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) w4[c] = wt[c];
+  float s[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float v = fmaxf(__uint_as_float(a[0][c]), 0.f) * w4[c].x;
+    if (HI > 1) v = fmaf(fmaxf(__uint_as_float(a[1 % HI][c]), 0.f), w4[c].y, v);
+    if (HI > 2) v = fmaf(fmaxf(__uint_as_float(a[2 % HI][c]), 0.f), w4[c].z, v);
+    if (HI > 3) v = fmaf(fmaxf(__uint_as_float(a[3 % HI][c]), 0.f), w4[c].w, v);
+    s[c] = v + 0.f;  // -0.0 -> +0.0
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    bool pass = s[c] >= tau;
+    if (GUARD) pass = pass && (col0 + c < S);
+    const uint32_t flag = pass ? 1u : 0u;
+    if (!kFastNoAppend) store_if(wp, flag, __float_as_uint(s[c]), static_cast<uint32_t>(col0 + c));
+    wp += flag;
+  }
+}
+
+template <int HI, bool GUARD>
+__device__ __forceinline__ void fast_reduce_tile(uint32_t taddr, const float4* wt, int col_base, int S, float tau,
+                                                 uint2*& wp, ProfClock& pc) {
+  uint32_t a0[HI][8], a1[HI][8];
+  fast_load_chunk<HI>(taddr, a0);
+  tmem_wait_ld();
+  pc.stop(4);
+#pragma unroll
+  for (int ch = 0; ch < BN / 8; ch += 2) {
+    fast_load_chunk<HI>(taddr + (ch + 1) * 8, a1);  // in flight while a0 is reduced
+    fast_reduce_chunk<HI, GUARD>(a0, wt + ch * 8, col_base + ch * 8, S, tau, wp);
+    pc.stop(5);
+    tmem_wait_ld();
+    pc.stop(4);
+    if (ch + 2 < BN / 8) fast_load_chunk<HI>(taddr + (ch + 2) * 8, a0);
+    fast_reduce_chunk<HI, GUARD>(a1, wt + (ch + 1) * 8, col_base + (ch + 1) * 8, S, tau, wp);
+    pc.stop(5);
+    if (ch + 2 < BN / 8) tmem_wait_ld();
+    pc.stop(4);
+  }
+}
+
+template <int HI>
+__global__ void __launch_bounds__(F_THREADS, 1)
+indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const IdxParams p,
+                    const uint32_t idesc) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* q_smem = smem;
+  unsigned char* k_smem = q_smem + HI * Q_HEAD_BYTES;
+  float4* w_smem = reinterpret_cast<float4*>(k_smem + NSTG * HI * K_HEAD_BYTES);
+  FastShared* sh = reinterpret_cast<FastShared*>(reinterpret_cast<unsigned char*>(w_smem) + WSLOTS * W_TILE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int blk_begin = p.row_begin / BM, blk_end = (p.row_end + BM - 1) / BM;  // this launch's row blocks
+  const int ntiles = (p.S + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sh->q_full, 1);
+    mbar_init(&sh->q_empty, 1);
+    for (int s = 0; s < NSTG; ++s) {
+      mbar_init(&sh->k_full[s], 1);
+      mbar_init(&sh->k_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh->acc_full[b], 1);
+      mbar_init(&sh->acc_empty[b], 4);
+    }
+    for (int s = 0; s < WSLOTS; ++s) {
+      mbar_init(&sh->w_full[s], 1);
+      mbar_init(&sh->w_empty[s], 4);
+    }
+    sh->abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) tmem_alloc(&sh->tmem_base, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer: Q block, key tiles, w*scale tiles ------------------------------
+    if (lane == 0) {
+      ProfClock pc((p.debug & 32) != 0);
+      uint32_t tuse = 0, nblk = 0;
+      for (int rb = blk_begin + blockIdx.x; rb < blk_end && !sh->abort_flag; rb += gridDim.x, ++nblk) {
+        pc.start();
+        if (!mbar_wait_bounded(&sh->q_empty, (nblk & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+        pc.stop(0);
+        mbar_arrive_expect_tx(&sh->q_full, HI * Q_HEAD_BYTES);
+#pragma unroll
+        for (int h = 0; h < HI; ++h) tma_load_2d(q_smem + h * Q_HEAD_BYTES, &tmQ, h * DI, rb * BM, &sh->q_full);
+        for (int j = 0; j < ntiles; ++j, ++tuse) {
+          const uint32_t s = tuse % NSTG, n = tuse / NSTG;
+          const uint32_t ws = tuse % WSLOTS, wn = tuse / WSLOTS;
+          pc.start();
+          if (!mbar_wait_bounded(&sh->k_empty[s], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          pc.stop(1);
+          if (!mbar_wait_bounded(&sh->w_empty[ws], (wn & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          pc.stop(2);
+          if (sh->abort_flag) break;
+          mbar_arrive_expect_tx(&sh->w_full[ws], W_TILE_BYTES);
+          bulk_g2s(w_smem + ws * BN, p.wsc + static_cast<size_t>(j) * BN, W_TILE_BYTES, &sh->w_full[ws]);
+          mbar_arrive_expect_tx(&sh->k_full[s], HI * K_HEAD_BYTES);
+#pragma unroll
+          for (int h = 0; h < HI; ++h)
+            tma_load_2d(k_smem + (s * HI + h) * K_HEAD_BYTES, &tmK, h * DI, j * BN, &sh->k_full[s]);
+          pc.stop(3);
+        }
+      }
+      pc.flush(warp);
+      if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      ProfClock pc((p.debug & 32) != 0);
+      uint32_t tuse = 0, nblk = 0, use0 = 0, use1 = 0;
+      for (int rb = blk_begin + blockIdx.x; rb < blk_end && !sh->abort_flag; rb += gridDim.x, ++nblk) {
+        pc.start();
+        if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
+        pc.stop(0);
+        for (int j = 0; j < ntiles; ++j, ++tuse) {
+          const uint32_t b = j & 1;
+          const uint32_t n = b ? use1 : use0;
+          pc.start();
+          if (!mbar_wait_bounded(&sh->acc_empty[b], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          pc.stop(1);
+          const uint32_t s = tuse % NSTG;
+          if (!mbar_wait_bounded(&sh->k_full[s], (tuse / NSTG) & 1u)) { sh->abort_flag = 1; break; }
+          pc.stop(2);
+          if (sh->abort_flag) break;
+          tc_fence_after();
+#pragma unroll
+          for (int h = 0; h < HI && !(p.debug & 16); ++h) {
+            const uint64_t adesc = make_smem_desc(smem_u32(q_smem + h * Q_HEAD_BYTES));
+            const uint64_t bdesc = make_smem_desc(smem_u32(k_smem + (s * HI + h) * K_HEAD_BYTES));
+            const uint32_t d = tmem_base + b * ACC_COLS + h * BN;
+#pragma unroll
+            for (int kk = 0; kk < DI / 16; ++kk) tc_mma_f16(d, adesc + 2 * kk, bdesc + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(&sh->k_empty[s]);
+          tc_commit(&sh->acc_full[b]);
+          if (b) ++use1; else ++use0;
+          pc.stop(3);
+        }
+        tc_commit(&sh->q_empty);
+      }
+      pc.flush(warp);
+      if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
+    }
+  } else {
+    // ------------------------------ epilogue: score, filter, append ------------------------------
+    const int e = warp - 2;
+    const int strm = e >> 2;
+    const int lq = warp & 3;
+    const int row_in_tile = lq * 32 + lane;
+    const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + strm * ACC_COLS;
+    const bool last_partial = (p.S % BN) != 0;
+    uint32_t acc_use = 0, nblk = 0;
+    ProfClock pc((p.debug & 32) != 0);
+    for (int rb = blk_begin + blockIdx.x; rb < blk_end; rb += gridDim.x, ++nblk) {
+      const int row = rb * BM + row_in_tile;
+      const bool active = row < p.T;
+      const float tau = active ? p.tau_in[row] : INFINITY;
+      const size_t lrow = static_cast<size_t>(row - p.row_begin);
+      uint2* const buf = p.cand + (lrow * 2 + strm) * p.caph;
+      uint2* wp = buf;
+      bool overflowed = false;
+      const uint32_t tile0 = nblk * static_cast<uint32_t>(ntiles);
+      for (int j = strm; j < ntiles; j += 2) {
+        if (sh->abort_flag) break;
+        const uint32_t ws = (tile0 + j) % WSLOTS, wn = (tile0 + j) / WSLOTS;
+        pc.start();
+        if (!mbar_wait_bounded(&sh->acc_full[strm], acc_use & 1u)) { sh->abort_flag = 1; break; }
+        pc.stop(1);
+        if (!mbar_wait_bounded(&sh->w_full[ws], wn & 1u)) { sh->abort_flag = 1; break; }
+        pc.stop(2);
+        tc_fence_after();
+        // a list without room for a whole tile is given up (the row is redone by the robust kernel): keep
+        // counting from the start of the list so that no store ever leaves it
+        if (wp - buf > p.caph - BN) {
+          overflowed = true;
+          wp = buf;
+        }
+        const float4* wt = w_smem + ws * BN;
+        if (last_partial && j == ntiles - 1)
+          fast_reduce_tile<HI, true>(taddr_row, wt, j * BN, p.S, tau, wp, pc);
+        else
+          fast_reduce_tile<HI, false>(taddr_row, wt, j * BN, p.S, tau, wp, pc);
+        tc_fence_before();
+        __syncwarp();
+        pc.stop(3);
+        if (lane == 0) {
+          mbar_arrive(&sh->acc_empty[strm]);
+          mbar_arrive(&sh->w_empty[ws]);
+        }
+        ++acc_use;
+      }
+      if (active) p.list_cnt[lrow * 2 + strm] = overflowed ? p.caph + 1 : static_cast<int>(wp - buf);
+      if (sh->abort_flag) break;
+    }
+    if (lane == 0) pc.flush(warp);
+    if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
+// exact top-k of every row's two lists (one warp per row, many warps per SM to hide the list reads)
+// ---------------------------------------------------------------------------------------------
+constexpr int FIN_WARPS = 8;
+
+struct IdxOutSink {
+  int32_t* oi;
+  void* os;
+  int dtype;
+  __device__ __forceinline__ void operator()(int pos, uint32_t bits, uint32_t idx) const {
+    oi[pos] = static_cast<int32_t>(idx);
+    if (os != nullptr) {
+      const float s = __uint_as_float(bits);
+      if (dtype == GW_BF16) static_cast<__nv_bfloat16*>(os)[pos] = __float2bfloat16_rn(s);
+      else if (dtype == GW_F16) static_cast<__half*>(os)[pos] = __float2half_rn(s);
+      else static_cast<float*>(os)[pos] = s;
+    }
+  }
+};
+
+__global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const IdxParams p) {
+  __shared__ TightSmem tsm[FIN_WARPS];
+  __shared__ SelectSmem<SEL_BINS> gsm;  // general routine, used by one warp at a time (rare fall-back)
+  __shared__ int gsm_lock;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) gsm_lock = 0;
+  __syncthreads();
+  const int row = p.row_begin + blockIdx.x * FIN_WARPS + w;
+  if (row >= p.row_end || row >= p.T) return;
+  const size_t lrow = static_cast<size_t>(row - p.row_begin);
+  const int n0 = p.list_cnt[lrow * 2], n1 = p.list_cnt[lrow * 2 + 1];
+  if (n0 > p.caph || n1 > p.caph || n0 + n1 < p.k) {  // overflowed, or tau was too high: redo from -inf
+    if (lane == 0) {
+      p.tau_redo[row] = -INFINITY;
+      p.block_flags[row / BM] = 1;
+    }
+    return;
+  }
+  if (lane == 0) p.tau_redo[row] = INFINITY;
+  if (p.debug & 1) return;
+  const uint2* b0 = p.cand + lrow * 2 * p.caph;
+  IdxOutSink sink{p.out_idx + static_cast<int64_t>(row) * p.k,
+                  p.out_scores ? static_cast<unsigned char*>(p.out_scores) +
+                                     static_cast<int64_t>(row) * p.k * (p.out_dtype == GW_F32 ? 4 : 2)
+                               : nullptr,
+                  p.out_dtype};
+  TightLists L{b0, n0, b0 + p.caph, n1};
+  const uint32_t lo = score_key(p.tau_in[row]), hi = score_key(p.smax_in[row]);
+  if (warp_select_tight(L, p.k, lo, hi, tsm[w], lane, sink, nullptr) == p.k) return;
+  // boundary bin too crowded (heavy ties): general selection, serialised over the CTA's one scratch area
+  bool got = false;
+  for (int spin = 0; spin < (1 << 22) && !got; ++spin) {
+    if (lane == 0) got = atomicCAS(&gsm_lock, 0, 1) == 0;
+    got = __shfl_sync(0xffffffffu, got, 0);
+    if (!got) __nanosleep(200);
+  }
+  if (!got) {
+    report_status(p.status, GW_ERR_TIMEOUT);
+    return;
+  }
+  TwoSegSrc src{b0, b0 + p.caph, n0};
+  FinalSink fsink{sink.oi, sink.os, sink.dtype};
+  group_select_topk<32, SEL_BINS, TwoSegSrc, FinalSink, 8>(src, n0 + n1, p.k, static_cast<unsigned long long>(lo) << 32,
+                                                           (static_cast<unsigned long long>(hi) << 32) | 0xffffffffull, gsm, lane, 0,
+                                                           fsink, nullptr, true);
+  __threadfence_block();
+  if (lane == 0) atomicExch(&gsm_lock, 0);
+}
+
+// tau = rank-th largest of each row of the sampled scores, smax = the row maximum (one warp per row)
+__global__ void __launch_bounds__(FIN_WARPS * 32) sample_threshold_kernel(const float* sc, int m, int64_t stride, int T, int rank,
+                                                                          float* tau, float* smax) {
+  __shared__ TightSmem tsm[FIN_WARPS];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * FIN_WARPS + w;
+  if (row >= T) return;
+  const float* r = sc + static_cast<int64_t>(row) * stride;
+  uint32_t kmin = 0xffffffffu, kmax = 0u;
+  for (int i = lane; i < m; i += 32) {
+    const uint32_t key = score_key(r[i]);
+    kmin = min(kmin, key);
+    kmax = max(kmax, key);
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, d));
+    kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, d));
+  }
+  TightDenseRow L{r, m};
+  uint32_t kth = 0;
+  auto none = [](int, uint32_t, uint32_t) {};
+  float t;
+  if (warp_select_tight(L, rank, kmin, kmax, tsm[w], lane, none, &kth) == rank) {
+    t = __uint_as_float(kth);
+  } else {
+    t = -INFINITY;  // pathological sample (a crowd of equal scores at the rank): no filtering for this row
+  }
+  if (lane == 0) {
+    tau[row] = t;
+    smax[row] = key_score(kmax);
+  }
+}
+
+inline size_t fast_smem_bytes(int Hi) {
+  return 1024 + static_cast<size_t>(Hi) * Q_HEAD_BYTES + static_cast<size_t>(NSTG) * Hi * K_HEAD_BYTES +
+         WSLOTS * W_TILE_BYTES + sizeof(FastShared);
+}
+
+}  // namespace
+}  // namespace gw

@@ -40,10 +40,12 @@ __device__ __forceinline__ void group_sync(int bar_id) {
 // `tid` is the caller's rank in the group (0..NT-1); all NT threads must call this together.
 // With NT == 32 sink may write into the storage src reads (in-place compaction): a write to pos never
 // targets a candidate that has not been read yet.
-template <int NT, int NB, class Src, class Sink>
+//   soft_hi       -> `hi` is only an estimate: candidates above it are counted in the top bin of the first level
+//   U             -> candidates fetched per thread before any is processed (hides the latency of src)
+template <int NT, int NB, class Src, class Sink, int U = 8>
 __device__ int group_select_topk(const Src& src, int n, int k, unsigned long long lo, unsigned long long hi,
                                  SelectSmem<NB>& sm, int tid, int bar_id, const Sink& sink,
-                                 unsigned long long* kth_out) {
+                                 unsigned long long* kth_out, bool soft_hi = false) {
   static_assert(NB % NT == 0, "bins must divide evenly over the group");
   constexpr int BPT = NB / NT;  // bins per thread
   constexpr int LOG_NB = (NB == 512) ? 9 : (NB == 1024) ? 10 : (NB == 2048) ? 11 : (NB == 4096) ? 12 : -1;
@@ -74,9 +76,21 @@ __device__ int group_select_topk(const Src& src, int n, int k, unsigned long lon
       for (int j = 0; j < BPT; ++j) sm.hist[tid + j * NT] = 0;
       if (tid == 0) sm.found = 0;
       group_sync<NT>(bar_id);
-      for (int i = tid; i < n; i += NT) {
-        const unsigned long long c = src(i);
-        if (c >= cur_lo && c <= cur_hi) atomicAdd(&sm.hist[static_cast<uint32_t>((c - cur_lo) >> shift)], 1u);
+      for (int base = tid; base < n; base += NT * U) {
+        unsigned long long c[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = base + u * NT;
+          c[u] = (i < n) ? src(i) : 0ull;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (base + u * NT < n && c[u] >= cur_lo && (c[u] <= cur_hi || soft_hi)) {
+            uint32_t bin = static_cast<uint32_t>((c[u] - cur_lo) >> shift);
+            if (soft_hi && (c[u] > cur_hi || bin > NB - 1)) bin = NB - 1;
+            atomicAdd(&sm.hist[bin], 1u);
+          }
+        }
       }
       group_sync<NT>(bar_id);
       // thread t owns bins NB-1-t*BPT ... NB-t*BPT-BPT (descending), so a scan over t walks bins downward
@@ -125,6 +139,8 @@ __device__ int group_select_topk(const Src& src, int n, int k, unsigned long lon
       const unsigned long long new_lo = cur_lo + (static_cast<unsigned long long>(b_star) << shift);
       unsigned long long new_hi = new_lo + ((1ull << shift) - 1ull);
       if (new_hi > cur_hi || new_hi < new_lo) new_hi = cur_hi;
+      if (soft_hi && b_star == NB - 1) new_hi = ~0ull;  // the top bin also holds everything above the estimate
+      soft_hi = false;
       kk -= static_cast<int>(above);
       cur_lo = new_lo;
       cur_hi = new_hi;
@@ -137,9 +153,19 @@ __device__ int group_select_topk(const Src& src, int n, int k, unsigned long lon
 
   // output pass
   unsigned long long my_min = ~0ull;
-  for (int base = 0; base < n; base += NT) {
+  for (int base0 = 0; base0 < n; base0 += NT * U) {
+   unsigned long long cu[U];
+#pragma unroll
+   for (int u = 0; u < U; ++u) {
+     const int i = base0 + u * NT + tid;
+     cu[u] = (i < n) ? src(i) : 0ull;
+   }
+#pragma unroll
+   for (int u = 0; u < U; ++u) {
+    const int base = base0 + u * NT;
+    if (base >= n) break;
     const int i = base + tid;
-    const unsigned long long c = (i < n) ? src(i) : 0ull;
+    const unsigned long long c = cu[u];
     bool take = false;
     if (i < n) {
       if (mode == 0) {
@@ -165,6 +191,7 @@ __device__ int group_select_topk(const Src& src, int n, int k, unsigned long lon
         my_min = c < my_min ? c : my_min;
       }
     }
+   }
   }
   if (mode == 1) {
     group_sync<NT>(bar_id);

@@ -64,6 +64,12 @@ int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const void* w, i
  * enough for the sampled threshold pass).  Host-only arithmetic; no reference counterpart. */
 int gw_indexer_topk_launch_count(int B, int T, int S, int k);
 
+/* Diagnostics: with the environment variable GW_IDX_DEBUG=32 the fused indexer kernel accumulates clock-cycle
+ * counters per CTA and warp role (waiting on each hand-off, issuing, reducing, selecting).  This call copies
+ * them to HOST memory (synchronising): [CTA][10 warps][8 slots] of 64-bit counts; returns the number of
+ * entries copied or a negative status.  No reference counterpart. */
+int gw_debug_indexer_profile(unsigned long long* host_out, int max_entries);
+
 /* Dense score block (debug / verification / threshold sampling): out[t, j] = score[t, j*key_step] for
  * j < ceil(S/key_step), fp32, row stride `out_row_stride` elements.  Same tensor-core main loop as the
  * fused call.  Replaces: sparse_topk_indexer.py:935-951 (_compute_scores_block_einsum) and the Triton
