@@ -9,7 +9,7 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libgeoweave_b200.so")
+LIB_PATH = os.environ.get("GEOWEAVE_B200_LIB") or os.path.join(HERE, "libgeoweave_b200.so")
 
 GW_F32, GW_BF16, GW_F16 = 0, 1, 2
 GW_OK = 0

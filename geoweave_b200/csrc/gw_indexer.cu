@@ -49,6 +49,7 @@ enum { MODE_TOPK = 0, MODE_SCORES = 1 };
 
 struct IdxParams {
   const float4* wsc;       // [S_pad] w * scale, four floats per key (heads beyond Hi are 0)
+  const float* wtile;      // fast path: w * scale per 64-key tile, [tile][4 heads][64]
   const float* tau_in;     // [T] initial thresholds, or null for -inf
   int32_t* out_idx;        // [T,k]
   void* out_scores;        // [T,k] of out_dtype, nullable
@@ -538,7 +539,7 @@ int cand_capacity(int k) {
 }
 
 struct WsLayout {
-  size_t wsc, tau0, smax, tau_redo, flags, sample, list_cnt, cand, total;
+  size_t wsc, wtile, tau0, smax, tau_redo, flags, sample, list_cnt, cand, total;
   int s_pad, m_pad, slots, caph, chunk_rows;
 };
 WsLayout ws_layout(int T, int S, int k) {
@@ -557,6 +558,7 @@ WsLayout ws_layout(int T, int S, int k) {
     return at;
   };
   L.wsc = take(static_cast<size_t>(L.s_pad) * 16);
+  L.wtile = take(sp.step > 0 ? (static_cast<size_t>(S) / FBN + 2) * W_TILE_BYTES : 0);
   L.tau0 = take(static_cast<size_t>(T) * 4);
   L.smax = take(static_cast<size_t>(T) * 4);
   L.tau_redo = take(static_cast<size_t>(T) * 4);
@@ -596,7 +598,7 @@ extern "C" size_t gw_indexer_topk_workspace_bytes(int B, int T, int S, int Hi, i
 }
 
 extern "C" int gw_debug_indexer_profile(unsigned long long* host_out, int max_entries) {
-  const int total = MAX_SLOTS * (F_THREADS / 32) * PROF_SLOTS;  // [CTA][10 warps][8 slots]
+  const int total = MAX_SLOTS * (F_THREADS / 32) * PROF_SLOTS;  // [CTA][11 warps][8 slots]
   const int n = max_entries < total ? max_entries : total;
   if (!host_out || n <= 0) return GW_ERR_INVALID_ARG;
   GW_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_idx_prof, sizeof(unsigned long long) * n));
@@ -609,7 +611,7 @@ extern "C" int gw_indexer_topk_launch_count(int B, int T, int S, int k) {
   const WsLayout L = ws_layout(T, S, k);
   if (L.chunk_rows == 0) return B * 2;
   const int chunks = (T + L.chunk_rows - 1) / L.chunk_rows;
-  return B * (4 + 2 * chunks);  // w scaling, sampled scores, thresholds, redo pass + (filter, finalize) per chunk
+  return B * (5 + 2 * chunks);  // 2 x w scaling, sampled scores, thresholds, redo pass + (filter, finalize) per chunk
 }
 
 extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
@@ -680,6 +682,7 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
   float* smax = reinterpret_cast<float*>(ws + L.smax);
   int* flags = reinterpret_cast<int*>(ws + L.flags);
   int* list_cnt = reinterpret_cast<int*>(ws + L.list_cnt);
+  float* wtile = reinterpret_cast<float*>(ws + L.wtile);
   float* sample = reinterpret_cast<float*>(ws + L.sample);
   uint2* cand = reinterpret_cast<uint2*>(ws + L.cand);
 
@@ -750,11 +753,24 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     p.tau_redo = tau_redo;
     p.block_flags = flags;
     p.list_cnt = list_cnt;
+    p.wtile = wtile;
+    {
+      const int ntiles = (S + FBN - 1) / FBN, n = ntiles * W_TILE_FLOATS;
+      if (dtype == GW_BF16)
+        prep_w_tiled_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(wb), S, Hi, scale, wtile, ntiles);
+      else
+        prep_w_tiled_kernel<__half><<<(n + 255) / 256, 256, 0, st>>>(reinterpret_cast<const __half*>(wb), S, Hi, scale, wtile, ntiles);
+      GW_LAUNCH_CHECK();
+    }
+    CUtensorMap mkf;
+    rc = make_map(&mkf, kb, dtype, S, Hi, row_bytes, FBN);
+    if (rc != GW_OK) return rc;
+    const uint32_t idesc_fast = make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, FBN);
     for (int r0 = 0; r0 < T; r0 += L.chunk_rows) {
       p.row_begin = r0;
       p.row_end = r0 + L.chunk_rows < T ? r0 + L.chunk_rows : T;
       const int cblocks = (p.row_end - p.row_begin + BM - 1) / BM;
-      rc = launch_indexer_fast(Hi, mq, mk, p, idesc, cblocks < sms ? cblocks : sms, st);
+      rc = launch_indexer_fast(Hi, mq, mkf, p, idesc_fast, cblocks < sms ? cblocks : sms, st);
       if (rc != GW_OK) return rc;
       finalize_lists_kernel<<<(p.row_end - p.row_begin + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(p);
       GW_LAUNCH_CHECK();

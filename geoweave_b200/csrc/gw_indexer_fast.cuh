@@ -1,11 +1,16 @@
 // Fast form of the fused indexer for large key sets, where a sampled per-row threshold tau is available.
 // (Included by gw_indexer.cu after IdxParams, the candidate sources/sinks and the tile constants.)
 //
-// Same tensor-core main loop as indexer_kernel, but the epilogue only filters: a thread appends (score, key)
-// to its row's list in global memory when score >= tau, through predicated stores and a moving pointer (no
-// divergent branch, no selection inside the kernel).  TMEM reads are software-pipelined (the next 8 columns
-// are in flight while 8 are reduced) and the w*scale tile comes from a small shared-memory ring that the TMA
-// producer fills alongside the keys.  The lists of all rows of a launch stay in the workspace and a second,
+// Tile shape: tcgen05.mma has a floor of about 48 cycles per instruction on B200 whatever N <= 96 is (measured:
+// 128x48, 128x64 and 128x96 steps all take 48 cycles, with the A operand in shared or in tensor memory), and
+// the Hi separate accumulators of a tile must fit twice into the 512 TMEM columns for the tensor cores to run
+// ahead of the epilogue, so N = 64 keys per tile with both operands in shared memory is the best available
+// point: 16 instructions = 768 cycles per 64-key tile, two thirds of the tensor peak.
+// The epilogue only filters: a thread appends (score, key) to its row's list in global memory when
+// score >= tau, through predicated stores at a moving offset (no divergent branch, no selection inside the
+// kernel).  TMEM reads are software-pipelined (the next 8 columns are in flight while 8 are reduced), the
+// head sum uses packed f32x2 arithmetic on column pairs, and the w*scale tile (stored head-major per tile)
+// comes from a small shared-memory ring that the TMA producer fills alongside the keys.  The lists of all rows of a launch stay in the workspace and a second,
 // occupancy-bound kernel (finalize_lists_kernel, one warp per row) turns each into the exact top-k.
 // A row whose list overflowed or holds fewer than k candidates is not resolved there: its row block is
 // flagged and the robust kernel redoes that block from tau = -inf.  The result is therefore exact for any
@@ -18,9 +23,14 @@ namespace gw {
 namespace {
 
 constexpr int F_EPI = 8;                        // epilogue warps (2 streams x 4 lane quarters)
-constexpr int F_THREADS = 64 + F_EPI * 32;      // 320
+constexpr int F_THREADS = 64 + F_EPI * 32 + 32; // 352: producer, MMA issuer 0, 8 epilogue warps, MMA issuer 1
+constexpr int FBN = 64;                         // keys per tile
+constexpr int FNSTG = 3;                        // key-tile ring depth
+constexpr int FK_HEAD_BYTES = FBN * DI * 2;     // 8 KB
+constexpr int F_ACC_COLS = 256;                 // TMEM columns per accumulator set (Hi * 64 <= 256)
 constexpr int WSLOTS = 8;                       // w*scale tile ring
-constexpr int W_TILE_BYTES = BN * 16;
+constexpr int W_TILE_FLOATS = 4 * FBN;          // [head][64] fp32
+constexpr int W_TILE_BYTES = W_TILE_FLOATS * 4; // 1 KB
 
 // Cycle counters for performance diagnosis (filled when bit 32 of IdxParams::debug is set, read back with
 // gw_debug_indexer_profile): per CTA, per warp, eight 64-bit slots.
@@ -41,8 +51,8 @@ struct ProfClock {
 };
 
 struct alignas(8) FastShared {
-  uint64_t q_full, q_empty;
-  uint64_t k_full[NSTG], k_empty[NSTG];
+  uint64_t q_full, q_empty;    // query block in shared memory: loaded / no longer read by any MMA
+  uint64_t k_full[FNSTG], k_empty[FNSTG];
   uint64_t acc_full[2], acc_empty[2];
   uint64_t w_full[WSLOTS], w_empty[WSLOTS];
   uint32_t tmem_base;
@@ -55,69 +65,119 @@ constexpr bool kFastNoAppend = true;
 constexpr bool kFastNoAppend = false;
 #endif
 
+// packed fp32 pairs (sm_100 f32x2 pipe): d = a * b + c on both halves
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
 template <int HI>
 __device__ __forceinline__ void fast_load_chunk(uint32_t taddr, uint32_t (&a)[HI][8]) {
 #pragma unroll
-  for (int h = 0; h < HI; ++h) tmem_ld_x8(taddr + h * BN, a[h]);
+  for (int h = 0; h < HI; ++h) tmem_ld_x8(taddr + h * FBN, a[h]);
 }
 
-// store (bits, col) at *ptr when flag is set; a predicated store, never a branch
-__device__ __forceinline__ void store_if(uint2* ptr, uint32_t flag, uint32_t bits, uint32_t col) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.u32 p, %0, 0;\n\t"
-      "@p st.global.v2.u32 [%1], {%2, %3};\n\t}" ::"r"(flag),
-      "l"(ptr), "r"(bits), "r"(col)
-      : "memory");
-}
-
-// reduce 8 columns held in `a`, append the ones that pass.  All loads and all arithmetic come first; the
-// appends are predicated stores through a moving pointer, so the code has no divergent branch.  The caller
-// guarantees room for 8 more entries.
-template <int HI, bool GUARD>
-__device__ __forceinline__ void fast_reduce_chunk(const uint32_t (&a)[HI][8], const float4* __restrict__ wt, int col0, int S,
-                                                  float tau, uint2*& wp) {
-  float4 w4[8];
-#pragma unroll
-  for (int c = 0; c < 8; ++c) w4[c] = wt[c];
-  float s[8];
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    float v = fmaxf(__uint_as_float(a[0][c]), 0.f) * w4[c].x;
-    if (HI > 1) v = fmaf(fmaxf(__uint_as_float(a[1 % HI][c]), 0.f), w4[c].y, v);
-    if (HI > 2) v = fmaf(fmaxf(__uint_as_float(a[2 % HI][c]), 0.f), w4[c].z, v);
-    if (HI > 3) v = fmaf(fmaxf(__uint_as_float(a[3 % HI][c]), 0.f), w4[c].w, v);
-    s[c] = v + 0.f;  // -0.0 -> +0.0
-  }
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    bool pass = s[c] >= tau;
-    if (GUARD) pass = pass && (col0 + c < S);
-    const uint32_t flag = pass ? 1u : 0u;
-    if (!kFastNoAppend) store_if(wp, flag, __float_as_uint(s[c]), static_cast<uint32_t>(col0 + c));
-    wp += flag;
+// Append (score, col) at *wp and advance wp when score >= tau (and col < S if GUARD): compare, predicated store and
+// predicated pointer bump in one block, so an append costs four instructions and never a branch.
+template <bool GUARD>
+__device__ __forceinline__ void append_if(uint2*& wp, float s, float tau, uint32_t col, int S) {
+#ifdef GW_FAST_SUM  // timing experiment: keep the arithmetic alive without any store
+  wp = reinterpret_cast<uint2*>(reinterpret_cast<unsigned long long>(wp) + __float_as_uint(s));
+  return;
+#endif
+  if (GUARD) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ge.f32 p, %1, %2;\n\t"
+        "setp.lt.and.s32 p, %4, %5, p;\n\t"
+        "@p st.global.v2.b32 [%0], {%3, %4};\n\t"
+        "@p add.u64 %0, %0, 8;\n\t}"
+        : "+l"(wp)
+        : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col), "r"(S));
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ge.f32 p, %1, %2;\n\t"
+        "@p st.global.v2.b32 [%0], {%3, %4};\n\t"
+        "@p add.u64 %0, %0, 8;\n\t}"
+        : "+l"(wp)
+        : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col));
   }
 }
 
+// Reduce 8 columns held in `a` and append the ones that pass.  wt = this tile's w*scale, [head][FBN]; c0 = first
+// column within the tile; col_g = its global key index.  All loads and arithmetic come first; the appends
+// are predicated stores at a moving 32-bit offset.  The caller guarantees room for 8 more entries.
 template <int HI, bool GUARD>
-__device__ __forceinline__ void fast_reduce_tile(uint32_t taddr, const float4* wt, int col_base, int S, float tau,
-                                                 uint2*& wp, ProfClock& pc) {
+__device__ __forceinline__ void fast_reduce_chunk(const uint32_t (&a)[HI][8], const float* __restrict__ wt, int c0, int col_g,
+                                                  int S, float tau, uint2*& wp) {
+  float2 acc[4];
+#pragma unroll
+  for (int h = 0; h < HI; ++h) {
+    const float4 wa = *reinterpret_cast<const float4*>(wt + h * FBN + c0);
+    const float4 wb = *reinterpret_cast<const float4*>(wt + h * FBN + c0 + 4);
+    float r[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      // 2 * relu(x) = x + |x| is one full-rate FADD (max() runs on the half-rate ALU pipe); the factor 2 is
+      // folded into the staged weights, which hold 0.5 * w * scale -- all exact powers of two
+      const float x = __uint_as_float(a[h][c]);
+      r[c] = x + fabsf(x);
+    }
+    const float2 w2[4] = {make_float2(wa.x, wa.y), make_float2(wa.z, wa.w), make_float2(wb.x, wb.y), make_float2(wb.z, wb.w)};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+#ifdef GW_FAST_SCALAR
+      acc[q].x = (h == 0) ? r[2 * q] * w2[q].x : fmaf(r[2 * q], w2[q].x, acc[q].x);
+      acc[q].y = (h == 0) ? r[2 * q + 1] * w2[q].y : fmaf(r[2 * q + 1], w2[q].y, acc[q].y);
+#else
+      const float2 r2 = make_float2(r[2 * q], r[2 * q + 1]);
+      acc[q] = (h == 0) ? fmul2(r2, w2[q]) : ffma2(r2, w2[q], acc[q]);
+#endif
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const float s = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+    if (!kFastNoAppend) append_if<GUARD>(wp, s, tau, static_cast<uint32_t>(col_g + c), S);
+  }
+}
+
+// One warp's half of a tile: columns c_begin .. c_begin + 31 (taddr already points at column c_begin of head 0)
+constexpr int F_HALF = FBN / 2;
+template <int HI, bool GUARD>
+__device__ __forceinline__ void fast_reduce_tile(uint32_t taddr, const float* wt, int c_begin, int col_base, int S, float tau,
+                                                 uint2*& wp) {
   uint32_t a0[HI][8], a1[HI][8];
   fast_load_chunk<HI>(taddr, a0);
   tmem_wait_ld();
-  pc.stop(4);
 #pragma unroll
-  for (int ch = 0; ch < BN / 8; ch += 2) {
+  for (int ch = 0; ch < F_HALF / 8; ch += 2) {
     fast_load_chunk<HI>(taddr + (ch + 1) * 8, a1);  // in flight while a0 is reduced
-    fast_reduce_chunk<HI, GUARD>(a0, wt + ch * 8, col_base + ch * 8, S, tau, wp);
-    pc.stop(5);
+    fast_reduce_chunk<HI, GUARD>(a0, wt, c_begin + ch * 8, col_base + c_begin + ch * 8, S, tau, wp);
     tmem_wait_ld();
-    pc.stop(4);
-    if (ch + 2 < BN / 8) fast_load_chunk<HI>(taddr + (ch + 2) * 8, a0);
-    fast_reduce_chunk<HI, GUARD>(a1, wt + (ch + 1) * 8, col_base + (ch + 1) * 8, S, tau, wp);
-    pc.stop(5);
-    if (ch + 2 < BN / 8) tmem_wait_ld();
-    pc.stop(4);
+    if (ch + 2 < F_HALF / 8) fast_load_chunk<HI>(taddr + (ch + 2) * 8, a0);
+    fast_reduce_chunk<HI, GUARD>(a1, wt, c_begin + (ch + 1) * 8, col_base + c_begin + (ch + 1) * 8, S, tau, wp);
+    if (ch + 2 < F_HALF / 8) tmem_wait_ld();
   }
 }
 
@@ -127,29 +187,29 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const uint32_t idesc) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* q_smem = smem;
-  unsigned char* k_smem = q_smem + HI * Q_HEAD_BYTES;
-  float4* w_smem = reinterpret_cast<float4*>(k_smem + NSTG * HI * K_HEAD_BYTES);
+  unsigned char* q_smem = smem;                                  // HI x 16 KB, 128-byte swizzled rows
+  unsigned char* k_smem = q_smem + HI * Q_HEAD_BYTES;            // FNSTG x HI x 6 KB
+  float* w_smem = reinterpret_cast<float*>(k_smem + FNSTG * HI * FK_HEAD_BYTES);
   FastShared* sh = reinterpret_cast<FastShared*>(reinterpret_cast<unsigned char*>(w_smem) + WSLOTS * W_TILE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int blk_begin = p.row_begin / BM, blk_end = (p.row_end + BM - 1) / BM;  // this launch's row blocks
-  const int ntiles = (p.S + BN - 1) / BN;
+  const int ntiles = (p.S + FBN - 1) / FBN;
 
   if (threadIdx.x == 0) {
     mbar_init(&sh->q_full, 1);
-    mbar_init(&sh->q_empty, 1);
-    for (int s = 0; s < NSTG; ++s) {
+    mbar_init(&sh->q_empty, 2);
+    for (int s = 0; s < FNSTG; ++s) {
       mbar_init(&sh->k_full[s], 1);
       mbar_init(&sh->k_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sh->acc_full[b], 1);
-      mbar_init(&sh->acc_empty[b], 4);
+      mbar_init(&sh->acc_empty[b], F_EPI);
     }
     for (int s = 0; s < WSLOTS; ++s) {
       mbar_init(&sh->w_full[s], 1);
-      mbar_init(&sh->w_empty[s], 4);
+      mbar_init(&sh->w_empty[s], F_EPI);
     }
     sh->abort_flag = 0;
     mbar_fence_init();
@@ -174,7 +234,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int h = 0; h < HI; ++h) tma_load_2d(q_smem + h * Q_HEAD_BYTES, &tmQ, h * DI, rb * BM, &sh->q_full);
         for (int j = 0; j < ntiles; ++j, ++tuse) {
-          const uint32_t s = tuse % NSTG, n = tuse / NSTG;
+          const uint32_t s = tuse % FNSTG, n = tuse / FNSTG;
           const uint32_t ws = tuse % WSLOTS, wn = tuse / WSLOTS;
           pc.start();
           if (!mbar_wait_bounded(&sh->k_empty[s], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
@@ -183,48 +243,55 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           pc.stop(2);
           if (sh->abort_flag) break;
           mbar_arrive_expect_tx(&sh->w_full[ws], W_TILE_BYTES);
-          bulk_g2s(w_smem + ws * BN, p.wsc + static_cast<size_t>(j) * BN, W_TILE_BYTES, &sh->w_full[ws]);
-          mbar_arrive_expect_tx(&sh->k_full[s], HI * K_HEAD_BYTES);
+          bulk_g2s(w_smem + ws * W_TILE_FLOATS, p.wtile + static_cast<size_t>(j) * W_TILE_FLOATS, W_TILE_BYTES, &sh->w_full[ws]);
+          mbar_arrive_expect_tx(&sh->k_full[s], HI * FK_HEAD_BYTES);
 #pragma unroll
           for (int h = 0; h < HI; ++h)
-            tma_load_2d(k_smem + (s * HI + h) * K_HEAD_BYTES, &tmK, h * DI, j * BN, &sh->k_full[s]);
+            tma_load_2d(k_smem + (s * HI + h) * FK_HEAD_BYTES, &tmK, h * DI, j * FBN, &sh->k_full[s]);
           pc.stop(3);
         }
       }
       pc.flush(warp);
       if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
+  } else if (warp == 1 || warp == 2 + F_EPI) {
+    // ------------------------------ MMA issuers ------------------------------
+    // Two issuing threads, one per accumulator set (even / odd key tiles).  A tcgen05.commit stalls the issuing
+    // thread's next MMA until the committed ones have drained (measured: 63-73 instead of 48 cycles per MMA
+    // with one issuer committing every tile); a second issuer fills those gaps.
+    const uint32_t b = (warp == 1) ? 0u : 1u;
     if (lane == 0) {
       ProfClock pc((p.debug & 32) != 0);
-      uint32_t tuse = 0, nblk = 0, use0 = 0, use1 = 0;
+      uint32_t nblk = 0, use = 0;
+      const uint64_t adesc0 = make_smem_desc(smem_u32(q_smem));
+      const uint64_t bdesc00 = make_smem_desc(smem_u32(k_smem));
+      const uint32_t d0 = tmem_base + b * F_ACC_COLS;
       for (int rb = blk_begin + blockIdx.x; rb < blk_end && !sh->abort_flag; rb += gridDim.x, ++nblk) {
         pc.start();
         if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
         pc.stop(0);
-        for (int j = 0; j < ntiles; ++j, ++tuse) {
-          const uint32_t b = j & 1;
-          const uint32_t n = b ? use1 : use0;
+        const uint32_t tile0 = nblk * static_cast<uint32_t>(ntiles);
+        for (int j = b; j < ntiles; j += 2, ++use) {
+          const uint32_t tuse = tile0 + j;
           pc.start();
-          if (!mbar_wait_bounded(&sh->acc_empty[b], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_bounded(&sh->acc_empty[b], (use & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
           pc.stop(1);
-          const uint32_t s = tuse % NSTG;
-          if (!mbar_wait_bounded(&sh->k_full[s], (tuse / NSTG) & 1u)) { sh->abort_flag = 1; break; }
+          const uint32_t s = tuse % FNSTG;
+          if (!mbar_wait_bounded(&sh->k_full[s], (tuse / FNSTG) & 1u)) { sh->abort_flag = 1; break; }
           pc.stop(2);
           if (sh->abort_flag) break;
           tc_fence_after();
+          const uint64_t bdesc0 = bdesc00 + s * ((HI * FK_HEAD_BYTES) >> 4);
+          if (!(p.debug & 16)) {
 #pragma unroll
-          for (int h = 0; h < HI && !(p.debug & 16); ++h) {
-            const uint64_t adesc = make_smem_desc(smem_u32(q_smem + h * Q_HEAD_BYTES));
-            const uint64_t bdesc = make_smem_desc(smem_u32(k_smem + (s * HI + h) * K_HEAD_BYTES));
-            const uint32_t d = tmem_base + b * ACC_COLS + h * BN;
+            for (int h = 0; h < HI; ++h)
 #pragma unroll
-            for (int kk = 0; kk < DI / 16; ++kk) tc_mma_f16(d, adesc + 2 * kk, bdesc + 2 * kk, idesc, kk > 0 ? 1u : 0u);
+              for (int kk = 0; kk < DI / 16; ++kk)  // +32 bytes along K per step = +2 in the address field
+                tc_mma_f16(d0 + h * FBN, adesc0 + h * (Q_HEAD_BYTES >> 4) + 2 * kk, bdesc0 + h * (FK_HEAD_BYTES >> 4) + 2 * kk, idesc,
+                           kk > 0 ? 1u : 0u);
           }
           tc_commit(&sh->k_empty[s]);
           tc_commit(&sh->acc_full[b]);
-          if (b) ++use1; else ++use0;
           pc.stop(3);
         }
         tc_commit(&sh->q_empty);
@@ -238,9 +305,11 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int strm = e >> 2;
     const int lq = warp & 3;
     const int row_in_tile = lq * 32 + lane;
-    const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + strm * ACC_COLS;
-    const bool last_partial = (p.S % BN) != 0;
-    uint32_t acc_use = 0, nblk = 0;
+    // every warp works on every tile: stream 0 reduces its columns 0..31, stream 1 columns 32..63, so both
+    // accumulator sets are drained by all eight warps and the tensor cores never wait for half of them
+    const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + strm * F_HALF;
+    const bool last_partial = (p.S % FBN) != 0;
+    uint32_t use0 = 0, use1 = 0, nblk = 0;
     ProfClock pc((p.debug & 32) != 0);
     for (int rb = blk_begin + blockIdx.x; rb < blk_end; rb += gridDim.x, ++nblk) {
       const int row = rb * BM + row_in_tile;
@@ -249,36 +318,39 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const size_t lrow = static_cast<size_t>(row - p.row_begin);
       uint2* const buf = p.cand + (lrow * 2 + strm) * p.caph;
       uint2* wp = buf;
+      uint2* const wp_guard = buf + (p.caph - F_HALF);
       bool overflowed = false;
       const uint32_t tile0 = nblk * static_cast<uint32_t>(ntiles);
-      for (int j = strm; j < ntiles; j += 2) {
+      for (int j = 0; j < ntiles; ++j) {
         if (sh->abort_flag) break;
+        const uint32_t b = j & 1;
+        const uint32_t n = b ? use1 : use0;
         const uint32_t ws = (tile0 + j) % WSLOTS, wn = (tile0 + j) / WSLOTS;
         pc.start();
-        if (!mbar_wait_bounded(&sh->acc_full[strm], acc_use & 1u)) { sh->abort_flag = 1; break; }
+        if (!mbar_wait_bounded(&sh->acc_full[b], n & 1u)) { sh->abort_flag = 1; break; }
         pc.stop(1);
         if (!mbar_wait_bounded(&sh->w_full[ws], wn & 1u)) { sh->abort_flag = 1; break; }
         pc.stop(2);
         tc_fence_after();
-        // a list without room for a whole tile is given up (the row is redone by the robust kernel): keep
+        // a list without room for a whole half tile is given up (the row is redone by the robust kernel): keep
         // counting from the start of the list so that no store ever leaves it
-        if (wp - buf > p.caph - BN) {
+        if (wp > wp_guard) {
           overflowed = true;
           wp = buf;
         }
-        const float4* wt = w_smem + ws * BN;
+        const float* wt = w_smem + ws * W_TILE_FLOATS;
         if (last_partial && j == ntiles - 1)
-          fast_reduce_tile<HI, true>(taddr_row, wt, j * BN, p.S, tau, wp, pc);
+          fast_reduce_tile<HI, true>(taddr_row + b * F_ACC_COLS, wt, strm * F_HALF, j * FBN, p.S, tau, wp);
         else
-          fast_reduce_tile<HI, false>(taddr_row, wt, j * BN, p.S, tau, wp, pc);
+          fast_reduce_tile<HI, false>(taddr_row + b * F_ACC_COLS, wt, strm * F_HALF, j * FBN, p.S, tau, wp);
         tc_fence_before();
         __syncwarp();
         pc.stop(3);
         if (lane == 0) {
-          mbar_arrive(&sh->acc_empty[strm]);
+          mbar_arrive(&sh->acc_empty[b]);
           mbar_arrive(&sh->w_empty[ws]);
         }
-        ++acc_use;
+        if (b) ++use1; else ++use0;
       }
       if (active) p.list_cnt[lrow * 2 + strm] = overflowed ? p.caph + 1 : static_cast<int>(wp - buf);
       if (sh->abort_flag) break;
@@ -396,8 +468,19 @@ __global__ void __launch_bounds__(FIN_WARPS * 32) sample_threshold_kernel(const 
   }
 }
 
+// 0.5 * w * scale as fp32 in the tile layout the fast kernel stages: [tile][head 0..3][64], zero beyond S and Hi
+// (the epilogue multiplies it with 2 * relu(acc))
+template <typename T>
+__global__ void prep_w_tiled_kernel(const T* w, int S, int Hi, float scale, float* wtile, int ntiles) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= ntiles * W_TILE_FLOATS) return;
+  const int tile = i / W_TILE_FLOATS, h = (i % W_TILE_FLOATS) / FBN, c = i % FBN;
+  const int s = tile * FBN + c;
+  wtile[i] = (s < S && h < Hi) ? to_float(w[static_cast<size_t>(s) * Hi + h]) * scale * 0.5f : 0.f;
+}
+
 inline size_t fast_smem_bytes(int Hi) {
-  return 1024 + static_cast<size_t>(Hi) * Q_HEAD_BYTES + static_cast<size_t>(NSTG) * Hi * K_HEAD_BYTES +
+  return 1024 + static_cast<size_t>(Hi) * Q_HEAD_BYTES + static_cast<size_t>(FNSTG) * Hi * FK_HEAD_BYTES +
          WSLOTS * W_TILE_BYTES + sizeof(FastShared);
 }
 

@@ -66,7 +66,7 @@ int gw_indexer_topk_launch_count(int B, int T, int S, int k);
 
 /* Diagnostics: with the environment variable GW_IDX_DEBUG=32 the fused indexer kernel accumulates clock-cycle
  * counters per CTA and warp role (waiting on each hand-off, issuing, reducing, selecting).  This call copies
- * them to HOST memory (synchronising): [CTA][10 warps][8 slots] of 64-bit counts; returns the number of
+ * them to HOST memory (synchronising): [CTA][11 warps][8 slots] of 64-bit counts; returns the number of
  * entries copied or a negative status.  No reference counterpart. */
 int gw_debug_indexer_profile(unsigned long long* host_out, int max_entries);
 
