@@ -8,6 +8,7 @@
 // lanes of the head) and for the p.V accumulation.  Each warp runs its own NST-deep ring of one-key stages
 // (K row slice + V row slice) with one mbarrier per stage, so there is no CTA-wide synchronisation at all.
 #include <math.h>
+#include <stdlib.h>
 
 #include "gw_common.cuh"
 
@@ -292,6 +293,12 @@ __global__ void __launch_bounds__(WARPS * 32) sparse_attn_kernel(const AttnParam
   }
 }
 
+}  // namespace
+}  // namespace gw
+#include "gw_attn_mma.cuh"
+namespace gw {
+namespace {
+
 template <typename T, int D, int G, int MODE>
 int launch_attn(const AttnParams& p, cudaStream_t st) {
   constexpr int SEG = G * D * sizeof(T);
@@ -377,7 +384,17 @@ extern "C" int gw_sparse_attn_fwd(const void* q, const void* k, const void* v, c
   p.scale_log2 = scale * 1.4426950408889634f;
   p.kv_heads_contiguous = (k_strides[2] == D && v_strides[2] == D) ? 1 : 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int rc = dispatch_t<0>(p, dtype, D, G, st);
+  // 16-bit token-major rows of up to 2 KB go to the tensor-core kernel, everything else to the scalar one
+  const char* force_scalar = getenv("GW_ATTN_SCALAR");
+  const bool use_mma = dtype != GW_F32 && D == 64 && (H == 8 || H == 16) && p.kv_heads_contiguous &&
+                       !(force_scalar && force_scalar[0] == '1');
+  int rc;
+  if (use_mma) {
+    if (dtype == GW_BF16) rc = (H == 16) ? launch_attn_mma<__nv_bfloat16, 2>(p, st) : launch_attn_mma<__nv_bfloat16, 1>(p, st);
+    else rc = (H == 16) ? launch_attn_mma<__half, 2>(p, st) : launch_attn_mma<__half, 1>(p, st);
+  } else {
+    rc = dispatch_t<0>(p, dtype, D, G, st);
+  }
   if (rc != GW_OK) return rc;
   if (attn_sum != nullptr) {
     if (H / G > 1) GW_CUDA_TRY(cudaMemsetAsync(attn_sum, 0, sizeof(float) * static_cast<size_t>(B) * T * K, st));

@@ -46,7 +46,8 @@ def test_bhtd_layout_and_strided_views(golden, name):
     qb, kb, vb = [x.transpose(1, 2).contiguous() for x in (q, k, v)]
     o_b, _ = sparse_index_flash_attn_inference_bhtd_func(qb, kb, vb, idx, None, False, float(c["scale"]), False)
     assert o_b.shape == qb.shape
-    assert torch.equal(o_b.transpose(1, 2), o_ref)  # same arithmetic, only the gather differs
+    # head-major input runs the scalar kernel, token-major the tensor-core one: equal up to output rounding
+    assert (o_b.transpose(1, 2).float() - o_ref.float()).abs().max().item() <= BF16_TOL
     # q/k/v as views of one fused [B,N,3,H,D] projection buffer, the layout DSAAttention produces
     if q.shape[1] == k.shape[1]:
         fused = torch.stack([q, k, v], dim=2).contiguous()
