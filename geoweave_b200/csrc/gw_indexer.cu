@@ -124,7 +124,8 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   IdxShared* sh = reinterpret_cast<IdxShared*>(sel + EPI_WARPS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nwork = (p.T + BM - 1) / BM;
+  const int nwork = ((p.row_end > 0 ? p.row_end : p.T) + BM - 1) / BM;
+  const int work0 = p.row_begin / BM;  // a launch may cover a range of rows (both multiples of the row block)
   const int ntiles = (p.S + BN - 1) / BN;
 
   if (threadIdx.x == 0) {
@@ -152,7 +153,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t kuse = 0, nblk = 0;
-      for (int wi = blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x) {
+      for (int wi = work0 + blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x) {
         if (p.block_flags && !p.block_flags[wi]) continue;
         const int rb = wi;
         if (!mbar_wait_bounded(&sh->q_empty, (nblk & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
@@ -176,7 +177,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       uint32_t kuse = 0, nblk = 0, use0 = 0, use1 = 0;
-      for (int wi = blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x) {
+      for (int wi = work0 + blockIdx.x; wi < nwork && !sh->abort_flag; wi += gridDim.x) {
         if (p.block_flags && !p.block_flags[wi]) continue;
         if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
         ++nblk;
@@ -218,7 +219,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                              : nullptr;
     const int compact_at = p.caph - BN;
 
-    for (int wi = blockIdx.x; wi < nwork; wi += gridDim.x) {
+    for (int wi = work0 + blockIdx.x; wi < nwork; wi += gridDim.x) {
       if (p.block_flags && !p.block_flags[wi]) continue;
       const int rb = wi;
       const int row = rb * BM + row_in_tile;
@@ -519,12 +520,19 @@ struct SamplePlan {
 SamplePlan plan_sample(int S, int k) {
   SamplePlan sp{0, 0, 0};
   if (S < 4096 || static_cast<int64_t>(S) < 8ll * k) return sp;
-  int step = S / 1024;
+  // every step-th key is sampled.  The count of keys above the rank-th sampled score scatters like
+  // step * sqrt(rank), so the relative precision of the estimate is set by k / step: keep it near 32, with at
+  // least 1024 sampled keys and at most one key in 16 (the sampled pass is extra tensor-core work)
+  int step = k / 32;
+  if (step < 16) step = 16;
+  if (step > S / 1024) step = S / 1024;
   if (step < 2) return sp;
   step |= 1;  // odd: never in lock-step with an even token grid
   const int m = (S + step - 1) / step;
   const double ratio = static_cast<double>(k) / step;
-  const int rank = static_cast<int>(ceil(ratio + 6.0 * sqrt(ratio) + 2.0));
+  // a row that comes up short costs a slow redo of its whole row block, so aim about 4.7 standard deviations
+  // above k (rank - ratio = 6.75 sqrt(ratio) is 4.7 sqrt(rank) at ratio 32)
+  const int rank = static_cast<int>(ceil(ratio + 6.75 * sqrt(ratio) + 2.0));
   if (rank * 2 >= m) return sp;
   sp.step = step;
   sp.m = m;
@@ -532,9 +540,18 @@ SamplePlan plan_sample(int S, int k) {
   return sp;
 }
 
-int cand_capacity(int k) {
+// list capacity per (row, stream).  The robust kernel keeps up to k after a compaction and refills to 2k; the fast
+// kernel needs room for the candidates the sampled threshold lets through: rank * step expected, scatter
+// step * sqrt(rank), split over two streams with some imbalance.
+int cand_capacity(int S, int k) {
   int c = 2 * k;
   if (c < 1024) c = 1024;
+  const SamplePlan sp = plan_sample(S, k);
+  if (sp.step > 0) {
+    const double total = static_cast<double>(sp.rank) * sp.step + 7.0 * sp.step * sqrt(static_cast<double>(sp.rank));
+    const int need = static_cast<int>(total * 0.5 * 1.15) + 2 * FBN;
+    if (need > c) c = need;
+  }
   return static_cast<int>(round_up(static_cast<size_t>(c), 64));
 }
 
@@ -549,7 +566,7 @@ WsLayout ws_layout(int T, int S, int k) {
   // the sampled pass reads w at key j*step for j up to the end of its last tile
   L.s_pad = static_cast<int>(round_up(static_cast<size_t>(S), BN)) + BN * (sp.step > 1 ? sp.step : 1) + BN;
   L.slots = nblocks < MAX_SLOTS ? nblocks : MAX_SLOTS;
-  L.caph = cand_capacity(k);
+  L.caph = cand_capacity(S, k);
   L.m_pad = static_cast<int>(round_up(static_cast<size_t>(sp.m), 4));
   size_t off = 0;
   auto take = [&](size_t bytes) {
@@ -563,7 +580,6 @@ WsLayout ws_layout(int T, int S, int k) {
   L.smax = take(static_cast<size_t>(T) * 4);
   L.tau_redo = take(static_cast<size_t>(T) * 4);
   L.flags = take(static_cast<size_t>(nblocks) * 4);
-  L.sample = take(static_cast<size_t>(T) * L.m_pad * 4);
   // fast path: the lists of all rows of a launch are kept until the finalize kernel has run, so long inputs are
   // processed in chunks of whole waves of row blocks (about 2 GiB of lists per chunk)
   const size_t row_bytes = static_cast<size_t>(2) * L.caph * 8;
@@ -572,6 +588,7 @@ WsLayout ws_layout(int T, int S, int k) {
   if (chunk_blocks > nblocks) chunk_blocks = nblocks;
   L.chunk_rows = sp.step > 0 ? chunk_blocks * BM : 0;
   L.list_cnt = take(static_cast<size_t>(L.chunk_rows) * 2 * 4);
+  L.sample = take(static_cast<size_t>(L.chunk_rows) * L.m_pad * 4);  // sampled scores of one chunk of rows
   const size_t robust_rows = static_cast<size_t>(L.slots) * BM;
   L.cand = take((robust_rows > static_cast<size_t>(L.chunk_rows) ? robust_rows : static_cast<size_t>(L.chunk_rows)) * row_bytes);
   L.total = off;
@@ -599,10 +616,14 @@ extern "C" size_t gw_indexer_topk_workspace_bytes(int B, int T, int S, int Hi, i
 
 extern "C" int gw_debug_indexer_profile(unsigned long long* host_out, int max_entries) {
   const int total = MAX_SLOTS * (F_THREADS / 32) * PROF_SLOTS;  // [CTA][11 warps][8 slots]
-  const int n = max_entries < total ? max_entries : total;
-  if (!host_out || n <= 0) return GW_ERR_INVALID_ARG;
-  GW_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_idx_prof, sizeof(unsigned long long) * n));
-  return n;
+  if (!host_out || max_entries < 4) return GW_ERR_INVALID_ARG;
+  // first four entries: finalize statistics since the last call (overflowed / short / general / lean rows)
+  GW_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_fin_stats, sizeof(unsigned long long) * 4));
+  const unsigned long long zero[4] = {0, 0, 0, 0};
+  GW_CUDA_TRY(cudaMemcpyToSymbol(g_fin_stats, zero, sizeof(zero)));
+  const int n = max_entries - 4 < total ? max_entries - 4 : total;
+  if (n > 0) GW_CUDA_TRY(cudaMemcpyFromSymbol(host_out + 4, g_idx_prof, sizeof(unsigned long long) * n));
+  return n + 4;
 }
 
 extern "C" int gw_indexer_topk_launch_count(int B, int T, int S, int k) {
@@ -611,7 +632,7 @@ extern "C" int gw_indexer_topk_launch_count(int B, int T, int S, int k) {
   const WsLayout L = ws_layout(T, S, k);
   if (L.chunk_rows == 0) return B * 2;
   const int chunks = (T + L.chunk_rows - 1) / L.chunk_rows;
-  return B * (5 + 2 * chunks);  // 2 x w scaling, sampled scores, thresholds, redo pass + (filter, finalize) per chunk
+  return B * (3 + 4 * chunks);  // 2 x w scaling, redo pass + (sampled scores, thresholds, filter, finalize) per chunk
 }
 
 extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
@@ -704,25 +725,6 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     rc = make_map(&mq, qb, dtype, T, Hi, row_bytes, BM);
     if (rc != GW_OK) return rc;
 
-    if (sp.step > 0) {
-      // threshold estimate: dense scores against every step-th key, then their rank-th largest per row
-      CUtensorMap ms;
-      rc = make_map(&ms, kb, dtype, sp.m, Hi, row_bytes * sp.step, BN);
-      if (rc != GW_OK) return rc;
-      IdxParams ps{};
-      ps.wsc = wsc;
-      ps.dense_out = sample;
-      ps.dense_stride = L.m_pad;
-      ps.T = T;
-      ps.S = sp.m;
-      ps.key_step = sp.step;
-      ps.status = status_dev;
-      rc = launch_indexer<MODE_SCORES>(Hi, mq, ms, ps, idesc, grid, st);
-      if (rc != GW_OK) return rc;
-      sample_threshold_kernel<<<(T + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(sample, sp.m, L.m_pad, T, sp.rank, tau0, smax);
-      GW_LAUNCH_CHECK();
-    }
-
     rc = make_map(&mk, kb, dtype, S, Hi, row_bytes, BN);
     if (rc != GW_OK) return rc;
     IdxParams p{};
@@ -766,10 +768,33 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     rc = make_map(&mkf, kb, dtype, S, Hi, row_bytes, FBN);
     if (rc != GW_OK) return rc;
     const uint32_t idesc_fast = make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, FBN);
+    CUtensorMap ms;
+    rc = make_map(&ms, kb, dtype, sp.m, Hi, row_bytes * sp.step, BN);
+    if (rc != GW_OK) return rc;
     for (int r0 = 0; r0 < T; r0 += L.chunk_rows) {
       p.row_begin = r0;
       p.row_end = r0 + L.chunk_rows < T ? r0 + L.chunk_rows : T;
       const int cblocks = (p.row_end - p.row_begin + BM - 1) / BM;
+      const int crows = p.row_end - p.row_begin;
+      {
+        // threshold estimate for this chunk of rows: dense scores against every step-th key, then their
+        // rank-th largest per row
+        IdxParams ps{};
+        ps.wsc = wsc;
+        ps.dense_out = sample - static_cast<int64_t>(r0) * L.m_pad;  // the kernel indexes rows globally
+        ps.dense_stride = L.m_pad;
+        ps.T = T;
+        ps.S = sp.m;
+        ps.key_step = sp.step;
+        ps.row_begin = p.row_begin;
+        ps.row_end = p.row_end;
+        ps.status = status_dev;
+        rc = launch_indexer<MODE_SCORES>(Hi, mq, ms, ps, idesc, cblocks < grid ? cblocks : grid, st);
+        if (rc != GW_OK) return rc;
+        sample_threshold_kernel<<<(crows + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(sample, sp.m, L.m_pad, crows, sp.rank,
+                                                                                             tau0 + r0, smax + r0);
+        GW_LAUNCH_CHECK();
+      }
       rc = launch_indexer_fast(Hi, mq, mkf, p, idesc_fast, cblocks < sms ? cblocks : sms, st);
       if (rc != GW_OK) return rc;
       finalize_lists_kernel<<<(p.row_end - p.row_begin + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(p);
@@ -781,6 +806,8 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     pr.smax_in = nullptr;
     pr.tau_redo = nullptr;
     pr.list_cnt = nullptr;
+    pr.row_begin = 0;
+    pr.row_end = 0;
     pr.debug = 0;
     rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, pr, idesc, grid, st);
     if (rc != GW_OK) return rc;

@@ -37,6 +37,10 @@ constexpr int W_TILE_BYTES = W_TILE_FLOATS * 4; // 1 KB
 constexpr int PROF_SLOTS = 8;
 __device__ unsigned long long g_idx_prof[MAX_SLOTS * (F_THREADS / 32) * PROF_SLOTS];  // [CTA][warp][slot]
 
+// finalize statistics (always counted; 4 cheap atomics per row at most): rows whose lists overflowed, rows that
+// came up short, rows that needed the general selection, rows finished by the lean selection
+__device__ unsigned long long g_fin_stats[4];
+
 struct ProfClock {
   unsigned long long acc[PROF_SLOTS] = {};
   long long t0 = 0;
@@ -398,6 +402,7 @@ __global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const Id
   const int n0 = p.list_cnt[lrow * 2], n1 = p.list_cnt[lrow * 2 + 1];
   if (n0 > p.caph || n1 > p.caph || n0 + n1 < p.k) {  // overflowed, or tau was too high: redo from -inf
     if (lane == 0) {
+      atomicAdd(&g_fin_stats[(n0 > p.caph || n1 > p.caph) ? 0 : 1], 1ull);
       p.tau_redo[row] = -INFINITY;
       p.block_flags[row / BM] = 1;
     }
@@ -413,7 +418,11 @@ __global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const Id
                   p.out_dtype};
   TightLists L{b0, n0, b0 + p.caph, n1};
   const uint32_t lo = score_key(p.tau_in[row]), hi = score_key(p.smax_in[row]);
-  if (warp_select_tight(L, p.k, lo, hi, tsm[w], lane, sink, nullptr) == p.k) return;
+  if (warp_select_tight(L, p.k, lo, hi, tsm[w], lane, sink, nullptr) == p.k) {
+    if (lane == 0) atomicAdd(&g_fin_stats[3], 1ull);
+    return;
+  }
+  if (lane == 0) atomicAdd(&g_fin_stats[2], 1ull);
   // boundary bin too crowded (heavy ties): general selection, serialised over the CTA's one scratch area
   bool got = false;
   for (int spin = 0; spin < (1 << 22) && !got; ++spin) {

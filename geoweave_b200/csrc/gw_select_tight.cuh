@@ -53,71 +53,90 @@ struct TightDenseRow {
 template <class Lists, class Sink>
 __device__ int warp_select_tight(const Lists& L, int k, uint32_t lo, uint32_t hi, TightSmem& sm, int lane,
                                  const Sink& sink, uint32_t* kth_bits) {
-  const uint32_t span = hi > lo ? hi - lo : 0u;
-  const int bits = 32 - __clz(span);
-  const int shift = bits > 10 ? bits - 10 : 0;
+  // Up to three histogram levels: [lo, hi] is only a hint (keys outside are clamped into the end bins of the
+  // first level), and score keys are logarithmic in the score, so the first boundary bin can be crowded.
+  uint32_t cur_lo = lo, cur_hi = hi > lo ? hi : lo;
+  int kk = k;
+  uint32_t cntb = 0;
+  for (int level = 0; level < 3; ++level) {
+    const uint32_t span = cur_hi - cur_lo;
+    const int bits = 32 - __clz(span);
+    const int shift = bits > 10 ? bits - 10 : 0;
 #pragma unroll
-  for (int j = 0; j < (TS_BINS + TS_BINS / 32) / 32; ++j) sm.hist[lane + 32 * j] = 0;
-  __syncwarp();
-
-  // ---- pass 1: histogram ----
+    for (int j = 0; j < (TS_BINS + TS_BINS / 32) / 32; ++j) sm.hist[lane + 32 * j] = 0;
+    __syncwarp();
+    // ---- histogram of the undecided keys ----
 #pragma unroll 1
-  for (int seg = 0; seg < 2; ++seg) {
-    const int n = L.count(seg);
-    for (int base = lane; base < n; base += 32 * TS_U) {
-      uint32_t sb[TS_U];
+    for (int seg = 0; seg < 2; ++seg) {
+      const int n = L.count(seg);
+      for (int base = lane; base < n; base += 32 * TS_U) {
+        uint32_t sb[TS_U];
 #pragma unroll
-      for (int u = 0; u < TS_U; ++u) {
-        const int i = base + 32 * u;
-        sb[u] = i < n ? L.bits(seg, i) : 0u;
-      }
+        for (int u = 0; u < TS_U; ++u) {
+          const int i = base + 32 * u;
+          sb[u] = i < n ? L.bits(seg, i) : 0u;
+        }
 #pragma unroll
-      for (int u = 0; u < TS_U; ++u) {
-        if (base + 32 * u < n) {
-          const uint32_t bn = ts_bin(score_key(__uint_as_float(sb[u])), lo, shift);
-          atomicAdd(&sm.hist[bn + (bn >> 5)], 1u);
+        for (int u = 0; u < TS_U; ++u) {
+          if (base + 32 * u < n) {
+            const uint32_t key = score_key(__uint_as_float(sb[u]));
+            if (level == 0 || (key >= cur_lo && key <= cur_hi)) {
+              const uint32_t bn = ts_bin(key, cur_lo, shift);
+              atomicAdd(&sm.hist[bn + (bn >> 5)], 1u);
+            }
+          }
         }
       }
     }
-  }
-  __syncwarp();
-
-  // ---- scan from the top bin down: lane t owns bins 32t..32t+31 ----
-  uint32_t mysum = 0;
+    __syncwarp();
+    // ---- scan from the top bin down: lane t owns bins 32t..32t+31 ----
+    uint32_t mysum = 0;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) mysum += sm.hist[33 * lane + j];
-  uint32_t above = mysum;  // becomes the count in all lanes above this one
+    for (int j = 0; j < 32; ++j) mysum += sm.hist[33 * lane + j];
+    uint32_t above = mysum;  // becomes the count in all lanes above this one
 #pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const uint32_t v = __shfl_down_sync(0xffffffffu, above, d);
-    if (lane + d < 32) above += v;
-  }
-  above -= mysum;
-  const bool mine = above < static_cast<uint32_t>(k) && static_cast<uint32_t>(k) <= above + mysum;
-  const uint32_t owner_mask = __ballot_sync(0xffffffffu, mine);
-  if (owner_mask == 0) return -1;  // fewer than k entries: the caller guarantees this cannot happen
-  const int owner = __ffs(owner_mask) - 1;
-  uint32_t b_star = 0, cnt_above = 0, cntb = 0;
-  if (lane == owner) {
-    uint32_t run = above;
-    for (int j = 31; j >= 0; --j) {
-      const uint32_t c = sm.hist[33 * lane + j];
-      if (run + c >= static_cast<uint32_t>(k)) {
-        b_star = 32 * lane + j;
-        cnt_above = run;
-        cntb = c;
-        break;
-      }
-      run += c;
+    for (int d = 1; d < 32; d <<= 1) {
+      const uint32_t v = __shfl_down_sync(0xffffffffu, above, d);
+      if (lane + d < 32) above += v;
     }
+    above -= mysum;
+    const bool mine = above < static_cast<uint32_t>(kk) && static_cast<uint32_t>(kk) <= above + mysum;
+    const uint32_t owner_mask = __ballot_sync(0xffffffffu, mine);
+    if (owner_mask == 0) return -1;  // fewer than k entries: the caller guarantees this cannot happen
+    const int owner = __ffs(owner_mask) - 1;
+    uint32_t b_star = 0, cnt_above = 0;
+    cntb = 0;
+    if (lane == owner) {
+      uint32_t run = above;
+      for (int j = 31; j >= 0; --j) {
+        const uint32_t c = sm.hist[33 * lane + j];
+        if (run + c >= static_cast<uint32_t>(kk)) {
+          b_star = 32 * lane + j;
+          cnt_above = run;
+          cntb = c;
+          break;
+        }
+        run += c;
+      }
+    }
+    b_star = __shfl_sync(0xffffffffu, b_star, owner);
+    cnt_above = __shfl_sync(0xffffffffu, cnt_above, owner);
+    cntb = __shfl_sync(0xffffffffu, cntb, owner);
+    __syncwarp();
+    kk -= static_cast<int>(cnt_above);
+    // the boundary bin becomes the new range (the end bins of the first level are open-ended)
+    const uint32_t new_lo = (level == 0 && b_star == 0) ? 0u : cur_lo + (b_star << shift);
+    uint32_t new_hi = cur_lo + (b_star << shift) + ((1u << shift) - 1u);
+    if (new_hi > cur_hi || new_hi < cur_lo) new_hi = cur_hi;
+    if (level == 0 && b_star == TS_BINS - 1) new_hi = 0xffffffffu;
+    cur_lo = new_lo;
+    cur_hi = new_hi;
+    if (cntb <= TS_SIDE || shift == 0) break;
   }
-  b_star = __shfl_sync(0xffffffffu, b_star, owner);
-  cnt_above = __shfl_sync(0xffffffffu, cnt_above, owner);
-  cntb = __shfl_sync(0xffffffffu, cntb, owner);
   if (cntb > TS_SIDE) return -1;
-  const int need = k - static_cast<int>(cnt_above);  // entries to take from the boundary bin
+  const int need = kk;  // entries to take from the boundary range [cur_lo, cur_hi]
 
-  // ---- pass 2: emit everything above the boundary bin, stash the boundary bin ----
+  // ---- output pass: emit everything above the boundary range, stash the boundary range ----
   int out_n = 0, side_n = 0;
 #pragma unroll 1
   for (int seg = 0; seg < 2; ++seg) {
@@ -134,9 +153,8 @@ __device__ int warp_select_tight(const Lists& L, int k, uint32_t lo, uint32_t hi
         if (base0 + 32 * u >= n) break;
         const bool valid = base0 + 32 * u + lane < n;
         const uint32_t key = score_key(__uint_as_float(e[u].x));
-        const uint32_t bn = ts_bin(key, lo, shift);
-        const bool take = valid && bn > b_star;
-        const bool inb = valid && bn == b_star;
+        const bool take = valid && key > cur_hi;
+        const bool inb = valid && key >= cur_lo && key <= cur_hi;
         const uint32_t bt = __ballot_sync(0xffffffffu, take);
         const uint32_t bi = __ballot_sync(0xffffffffu, inb);
         const uint32_t lt = (1u << lane) - 1u;

@@ -66,8 +66,9 @@ int gw_indexer_topk_launch_count(int B, int T, int S, int k);
 
 /* Diagnostics: with the environment variable GW_IDX_DEBUG=32 the fused indexer kernel accumulates clock-cycle
  * counters per CTA and warp role (waiting on each hand-off, issuing, reducing, selecting).  This call copies
- * them to HOST memory (synchronising): [CTA][11 warps][8 slots] of 64-bit counts; returns the number of
- * entries copied or a negative status.  No reference counterpart. */
+ * them to HOST memory (synchronising): four finalize counters (rows whose candidate lists overflowed, came up
+ * short, needed the general selection, were finished by the lean selection; reset by this call), then
+ * [CTA][11 warps][8 slots] of 64-bit cycle counts; returns the number of entries copied or a negative status.  No reference counterpart. */
 int gw_debug_indexer_profile(unsigned long long* host_out, int max_entries);
 
 /* Dense score block (debug / verification / threshold sampling): out[t, j] = score[t, j*key_step] for
