@@ -190,7 +190,9 @@ def run_ours(args):
         host.append(t)
         resident.append({n: x.to(dev) for n, x in t.items()})
     out_host = [torch.empty((1, rows, H, D), dtype=bf).pin_memory() for _ in range(layers)]
-    staging = {n: torch.empty_like(x, device=dev) for n, x in host[0].items()}
+    # end-to-end arm: two device staging sets so that the copy of layer i+1 overlaps the kernels of layer i
+    staging = [{n: torch.empty_like(x, device=dev) for n, x in host[0].items()} for _ in range(2)]
+    copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     h2d = sum(x.numel() * x.element_size() for t in host for x in t.values())
     d2h = sum(x.numel() * x.element_size() for x in out_host)
 
@@ -219,11 +221,28 @@ def run_ours(args):
             layer_op(resident[layer], record)
 
     def step_e2e():
+        """Every layer: pinned host inputs -> device (copy stream), the three stages (main stream), output ->
+        pinned host (second copy stream); copies of neighbouring layers overlap the kernels."""
+        main = torch.cuda.current_stream(dev)
+        used = [None, None]  # event: kernels that read staging set i have finished
         for layer in range(layers):
-            for n, x in host[layer].items():
-                staging[n].copy_(x, non_blocking=True)
-            out = layer_op(staging, False)
-            out_host[layer].copy_(out, non_blocking=True)
+            st = staging[layer & 1]
+            with torch.cuda.stream(copy_in):
+                if used[layer & 1] is not None:
+                    copy_in.wait_event(used[layer & 1])
+                for n, x in host[layer].items():
+                    st[n].copy_(x, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(copy_in)
+            main.wait_event(ready)
+            out = layer_op(st, False)
+            done = torch.cuda.Event()
+            done.record(main)
+            used[layer & 1] = done
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done)
+                out_host[layer].copy_(out, non_blocking=True)
+                out.record_stream(copy_out)
         torch.cuda.synchronize()
 
     def barrier():

@@ -97,7 +97,13 @@ __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
 template <int HI>
 __device__ __forceinline__ void fast_load_chunk(uint32_t taddr, uint32_t (&a)[HI][8]) {
 #pragma unroll
+#ifdef GW_NO_TMEM_LD  // timing experiment: arithmetic on whatever the registers hold
+  for (int h = 0; h < HI; ++h)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) asm volatile("xor.b32 %0, %0, %1;" : "+r"(a[h][c]) : "r"(taddr));
+#else
   for (int h = 0; h < HI; ++h) tmem_ld_x8(taddr + h * FBN, a[h]);
+#endif
 }
 
 // Append (score, col) at *wp and advance wp when score >= tau (and col < S if GUARD): compare, predicated store and
@@ -118,6 +124,15 @@ __device__ __forceinline__ void append_if(uint2*& wp, float s, float tau, uint32
         : "+l"(wp)
         : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col), "r"(S));
   } else {
+#ifdef GW_APPEND_IMAD  // experiment: pointer bump as one wide multiply-add on the FMA pipe
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ge.f32 p, %1, %2;\n\t"
+        "@p st.global.v2.b32 [%0], {%3, %4};\n\t"
+        "@p mad.wide.u32 %0, %5, %6, %0;\n\t}"
+        : "+l"(wp)
+        : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col), "r"(8u), "r"(1u));
+#else
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ge.f32 p, %1, %2;\n\t"
@@ -125,6 +140,7 @@ __device__ __forceinline__ void append_if(uint2*& wp, float s, float tau, uint32
         "@p add.u64 %0, %0, 8;\n\t}"
         : "+l"(wp)
         : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col));
+#endif
   }
 }
 
@@ -137,8 +153,12 @@ __device__ __forceinline__ void fast_reduce_chunk(const uint32_t (&a)[HI][8], co
   float2 acc[4];
 #pragma unroll
   for (int h = 0; h < HI; ++h) {
+#ifdef GW_W_CONST  // timing experiment: no shared-memory reads of the weights
+    const float4 wa = make_float4(0.1f * h, 0.2f, 0.3f, 0.4f), wb = make_float4(0.5f, 0.6f, 0.7f, 0.8f + c0);
+#else
     const float4 wa = *reinterpret_cast<const float4*>(wt + h * FBN + c0);
     const float4 wb = *reinterpret_cast<const float4*>(wt + h * FBN + c0 + 4);
+#endif
     float r[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) {

@@ -161,3 +161,78 @@ def test_unsupported_arguments_fail_loudly():
         sparse_topk_indexer_func(q.float(), kx.float(), w.float(), None, 8, None, 0)
     sc, pos = score_topk_fused_select(q, kx, w, softmax_scale=0.125, out_pos=torch.empty(1, 10, 16, dtype=torch.int32, device=dev()))
     assert pos.shape == (1, 10, 16) and sc.shape == (1, 10, 16)
+
+
+def _finalize_counters():
+    """[overflowed, short, general, lean] rows seen by the finalize kernel since the last call."""
+    import ctypes
+
+    from geoweave_b200 import _lib
+
+    buf = (ctypes.c_ulonglong * 4)()
+    assert _lib.load().gw_debug_indexer_profile(buf, 4) == 4
+    return list(buf)
+
+
+def test_fast_path_is_the_one_that_runs_and_needs_no_redo():
+    """Large key set, generic data: every row is finished by the lean selection, none is flagged for the redo pass."""
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    q, kx, w = make_indexer_inputs(384, 16656, seed=77)
+    _finalize_counters()
+    idx, _ = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, 512, 0.125, 256)
+    geoweave_b200.check_status()
+    overflowed, short, general, lean = _finalize_counters()
+    assert (overflowed, short) == (0, 0) and general + lean == 384 and lean >= 380
+    res = orc.audit_topk(idx, orc.indexer_scores(q, kx, w, 0.125), 512, q, kx, w, 0.125)
+    assert res["unexplained"] == 0 and res["duplicates"] == 0, res
+
+
+def test_fast_path_heavy_ties_use_the_general_selection():
+    """Scores take few distinct values (small integers): the boundary bin of the lean selection is crowded, the
+    general routine takes over, and the lower-index rule still holds exactly."""
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    g = torch.Generator().manual_seed(5)
+    T, S, k = 256, 8328, 512
+    q = torch.randint(0, 2, (1, T, 4, 64), generator=g).float().bfloat16()
+    kx = torch.randint(0, 2, (1, S, 4, 64), generator=g).float().bfloat16()
+    w = torch.ones(1, S, 4).bfloat16()
+    _finalize_counters()
+    idx, _ = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, k, 0.125, 256)
+    geoweave_b200.check_status()
+    counters = _finalize_counters()
+    assert torch.equal(sorted_idx(idx), orc.topk_tie_exact(orc.indexer_scores(q, kx, w, 0.125), k).long()), counters
+
+
+def test_fast_path_shortfall_and_overflow_rows_are_redone_exactly():
+    """Half of the keys carry a huge weight only in the second half of the key order, the sample sees them, but a
+    few query rows are all-zero (every score ties at 0): whatever the filter does with such rows, the result is exact."""
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    g = torch.Generator().manual_seed(6)
+    T, S, k = 200, 9000, 256
+    q = torch.randn(1, T, 4, 64, generator=g)
+    q[0, ::7] = 0.0  # rows whose scores are all exactly 0
+    kx = torch.randn(1, S, 4, 64, generator=g)
+    w = torch.rand(1, S, 4, generator=g)
+    w[0, S // 2:] *= 50.0
+    q, kx, w = q.bfloat16(), kx.bfloat16(), w.bfloat16()
+    idx, _ = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, k, 0.125, 256)
+    geoweave_b200.check_status()
+    scores = orc.indexer_scores(q, kx, w, 0.125)
+    res = orc.audit_topk(idx, scores, k, q, kx, w, 0.125)
+    assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
+    zero_rows = sorted_idx(idx)[0, ::7]
+    assert torch.equal(zero_rows, torch.arange(k).expand(zero_rows.shape[0], k))  # all ties: the k lowest indices
+
+
+def test_long_key_set_few_queries():
+    """T != S with a key set of 133248 (128 views): the chunked sample / filter / finalize path."""
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    q, kx, w = make_indexer_inputs(130, 133248, seed=8)
+    idx, _ = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, 1024, 0.125, 256)
+    geoweave_b200.check_status()
+    res = orc.audit_topk(idx, orc.indexer_scores(q, kx, w, 0.125), 1024, q, kx, w, 0.125)
+    assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
