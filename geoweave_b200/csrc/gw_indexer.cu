@@ -62,7 +62,8 @@ struct IdxParams {
   int key_step;            // score mode: column j is key j * key_step
   const float* smax_in;    // [T] fast path: estimate of the row maximum (binning range of the final selection)
   int row_begin, row_end;  // fast path: rows of this launch (row_begin a multiple of the row block)
-  int* list_cnt;           // fast path: [rows of the launch][2] list lengths (caph + 1 = overflowed)
+  int* list_cnt;           // fast path: [rows of the launch][nsplit][2] list lengths (caph + 1 = overflowed)
+  int nsplit;              // fast path: key splits per row block (lists and their capacity caph are per split)
   int* block_flags;        // [row blocks] fast kernel: sets 1 for blocks with a row to redo; robust kernel, when
                            // non-null: processes only the flagged blocks
   float* tau_redo;         // [T] fast kernel output: -inf for rows to redo, +inf for finished rows
@@ -555,9 +556,26 @@ int cand_capacity(int S, int k) {
   return static_cast<int>(round_up(static_cast<size_t>(c), 64));
 }
 
+// Key splits per row block for a fast-path launch over `blocks` row blocks on `sms` SMs: the smallest split
+// count (up to 8) whose makespan, in units of one whole row block, is within 3 % of the best one.
+int plan_splits(int blocks, int sms, int ntiles) {
+  double best = 1e30;
+  double span[9];
+  for (int ns = 1; ns <= 8; ++ns) {
+    const long long items = static_cast<long long>(blocks) * ns;
+    span[ns] = static_cast<double>((items + sms - 1) / sms) / ns;
+    if (ns * 8 > ntiles) span[ns] = 1e30;  // keep at least 8 key tiles per item
+    if (span[ns] < best) best = span[ns];
+  }
+  for (int ns = 1; ns <= 8; ++ns)
+    if (span[ns] <= best * 1.03) return ns;
+  return 1;
+}
+constexpr int kPlanSms = 148;  // SM count assumed when sizing the workspace (any split count is valid on any device)
+
 struct WsLayout {
   size_t wsc, wtile, tau0, smax, tau_redo, flags, sample, list_cnt, cand, total;
-  int s_pad, m_pad, slots, caph, chunk_rows;
+  int s_pad, m_pad, slots, caph, chunk_rows, nsplit, cap_split;
 };
 WsLayout ws_layout(int T, int S, int k) {
   WsLayout L;
@@ -582,15 +600,21 @@ WsLayout ws_layout(int T, int S, int k) {
   L.flags = take(static_cast<size_t>(nblocks) * 4);
   // fast path: the lists of all rows of a launch are kept until the finalize kernel has run, so long inputs are
   // processed in chunks of whole waves of row blocks (about 2 GiB of lists per chunk)
-  const size_t row_bytes = static_cast<size_t>(2) * L.caph * 8;
-  int chunk_blocks = static_cast<int>((static_cast<size_t>(2) << 30) / row_bytes / BM);
-  chunk_blocks = chunk_blocks >= 2 * MAX_SLOTS ? chunk_blocks / 148 * 148 : (chunk_blocks > 0 ? chunk_blocks : 1);
+  const size_t robust_row_bytes = static_cast<size_t>(2) * L.caph * 8;
+  int chunk_blocks = static_cast<int>((static_cast<size_t>(2) << 30) / (robust_row_bytes * 5 / 4) / BM);
+  chunk_blocks = chunk_blocks >= 2 * MAX_SLOTS ? chunk_blocks / kPlanSms * kPlanSms : (chunk_blocks > 0 ? chunk_blocks : 1);
   if (chunk_blocks > nblocks) chunk_blocks = nblocks;
   L.chunk_rows = sp.step > 0 ? chunk_blocks * BM : 0;
-  L.list_cnt = take(static_cast<size_t>(L.chunk_rows) * 2 * 4);
+  // key splits even out a launch with few row blocks or a ragged last wave; every split gets its own lists,
+  // each with a 25 % larger share of the capacity than an even division would give
+  L.nsplit = sp.step > 0 ? plan_splits(chunk_blocks, kPlanSms, (S + FBN - 1) / FBN) : 1;
+  L.cap_split = L.nsplit == 1 ? L.caph : static_cast<int>(round_up(static_cast<size_t>(L.caph) * 5 / (4 * L.nsplit) + 2 * FBN, 64));
+  const size_t fast_row_bytes = static_cast<size_t>(L.nsplit) * 2 * L.cap_split * 8;
+  L.list_cnt = take(static_cast<size_t>(L.chunk_rows) * L.nsplit * 2 * 4);
   L.sample = take(static_cast<size_t>(L.chunk_rows) * L.m_pad * 4);  // sampled scores of one chunk of rows
-  const size_t robust_rows = static_cast<size_t>(L.slots) * BM;
-  L.cand = take((robust_rows > static_cast<size_t>(L.chunk_rows) ? robust_rows : static_cast<size_t>(L.chunk_rows)) * row_bytes);
+  const size_t robust_bytes = static_cast<size_t>(L.slots) * BM * robust_row_bytes;
+  const size_t fast_bytes = static_cast<size_t>(L.chunk_rows) * fast_row_bytes;
+  L.cand = take(robust_bytes > fast_bytes ? robust_bytes : fast_bytes);
   L.total = off;
   return L;
 }
@@ -756,6 +780,8 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     p.block_flags = flags;
     p.list_cnt = list_cnt;
     p.wtile = wtile;
+    p.nsplit = L.nsplit;
+    p.caph = L.cap_split;
     {
       const int ntiles = (S + FBN - 1) / FBN, n = ntiles * W_TILE_FLOATS;
       if (dtype == GW_BF16)
@@ -795,7 +821,8 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
                                                                                              tau0 + r0, smax + r0);
         GW_LAUNCH_CHECK();
       }
-      rc = launch_indexer_fast(Hi, mq, mkf, p, idesc_fast, cblocks < sms ? cblocks : sms, st);
+      const int citems = cblocks * L.nsplit;
+      rc = launch_indexer_fast(Hi, mq, mkf, p, idesc_fast, citems < sms ? citems : sms, st);
       if (rc != GW_OK) return rc;
       finalize_lists_kernel<<<(p.row_end - p.row_begin + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(p);
       GW_LAUNCH_CHECK();
@@ -806,6 +833,8 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     pr.smax_in = nullptr;
     pr.tau_redo = nullptr;
     pr.list_cnt = nullptr;
+    pr.nsplit = 1;
+    pr.caph = L.caph;
     pr.row_begin = 0;
     pr.row_end = 0;
     pr.debug = 0;

@@ -219,6 +219,11 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int blk_begin = p.row_begin / BM, blk_end = (p.row_end + BM - 1) / BM;  // this launch's row blocks
   const int ntiles = (p.S + FBN - 1) / FBN;
+  // work item = (row block, key split): a launch with fewer row blocks than SMs, or a ragged last wave, is
+  // evened out by cutting the key range of every row block into nsplit pieces that go to different CTAs
+  const int nsplit = p.nsplit;
+  const int tps = (ntiles + nsplit - 1) / nsplit;  // key tiles per split
+  const int nitems = (blk_end - blk_begin) * nsplit;
 
   if (threadIdx.x == 0) {
     mbar_init(&sh->q_full, 1);
@@ -250,14 +255,16 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0) {
       ProfClock pc((p.debug & 32) != 0);
       uint32_t tuse = 0, nblk = 0;
-      for (int rb = blk_begin + blockIdx.x; rb < blk_end && !sh->abort_flag; rb += gridDim.x, ++nblk) {
+      for (int item = blockIdx.x; item < nitems && !sh->abort_flag; item += gridDim.x, ++nblk) {
+        const int rb = blk_begin + item / nsplit, sp = item % nsplit;
+        const int t0 = sp * tps, t1 = (t0 + tps < ntiles) ? t0 + tps : ntiles;
         pc.start();
         if (!mbar_wait_bounded(&sh->q_empty, (nblk & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
         pc.stop(0);
         mbar_arrive_expect_tx(&sh->q_full, HI * Q_HEAD_BYTES);
 #pragma unroll
         for (int h = 0; h < HI; ++h) tma_load_2d(q_smem + h * Q_HEAD_BYTES, &tmQ, h * DI, rb * BM, &sh->q_full);
-        for (int j = 0; j < ntiles; ++j, ++tuse) {
+        for (int j = t0; j < t1; ++j, ++tuse) {
           const uint32_t s = tuse % FNSTG, n = tuse / FNSTG;
           const uint32_t ws = tuse % WSLOTS, wn = tuse / WSLOTS;
           pc.start();
@@ -286,17 +293,19 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t b = (warp == 1) ? 0u : 1u;
     if (lane == 0) {
       ProfClock pc((p.debug & 32) != 0);
-      uint32_t nblk = 0, use = 0;
+      uint32_t nblk = 0, use = 0, tbase = 0;
       const uint64_t adesc0 = make_smem_desc(smem_u32(q_smem));
       const uint64_t bdesc00 = make_smem_desc(smem_u32(k_smem));
       const uint32_t d0 = tmem_base + b * F_ACC_COLS;
-      for (int rb = blk_begin + blockIdx.x; rb < blk_end && !sh->abort_flag; rb += gridDim.x, ++nblk) {
+      for (int item = blockIdx.x; item < nitems && !sh->abort_flag; item += gridDim.x, ++nblk) {
+        const int sp = item % nsplit;
+        const int t0 = sp * tps, t1 = (t0 + tps < ntiles) ? t0 + tps : ntiles;
+        const int nt = t1 > t0 ? t1 - t0 : 0;
         pc.start();
         if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
         pc.stop(0);
-        const uint32_t tile0 = nblk * static_cast<uint32_t>(ntiles);
-        for (int j = b; j < ntiles; j += 2, ++use) {
-          const uint32_t tuse = tile0 + j;
+        for (int j = b; j < nt; j += 2, ++use) {
+          const uint32_t tuse = tbase + j;
           pc.start();
           if (!mbar_wait_bounded(&sh->acc_empty[b], (use & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
           pc.stop(1);
@@ -319,6 +328,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           pc.stop(3);
         }
         tc_commit(&sh->q_empty);
+        tbase += nt;
       }
       pc.flush(warp);
       if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
@@ -333,23 +343,27 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // accumulator sets are drained by all eight warps and the tensor cores never wait for half of them
     const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + strm * F_HALF;
     const bool last_partial = (p.S % FBN) != 0;
-    uint32_t use0 = 0, use1 = 0, nblk = 0;
+    uint32_t use0 = 0, use1 = 0, tbase = 0;
     ProfClock pc((p.debug & 32) != 0);
-    for (int rb = blk_begin + blockIdx.x; rb < blk_end; rb += gridDim.x, ++nblk) {
+    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+      const int rb = blk_begin + item / nsplit, sp = item % nsplit;
+      const int t0 = sp * tps, t1 = (t0 + tps < ntiles) ? t0 + tps : ntiles;
+      const int nt = t1 > t0 ? t1 - t0 : 0;
       const int row = rb * BM + row_in_tile;
       const bool active = row < p.T;
       const float tau = active ? p.tau_in[row] : INFINITY;
       const size_t lrow = static_cast<size_t>(row - p.row_begin);
-      uint2* const buf = p.cand + (lrow * 2 + strm) * p.caph;
+      const size_t seg = (lrow * nsplit + sp) * 2 + strm;  // this thread's list
+      uint2* const buf = p.cand + seg * p.caph;
       uint2* wp = buf;
       uint2* const wp_guard = buf + (p.caph - F_HALF);
       bool overflowed = false;
-      const uint32_t tile0 = nblk * static_cast<uint32_t>(ntiles);
-      for (int j = 0; j < ntiles; ++j) {
+      for (int jl = 0; jl < nt; ++jl) {
         if (sh->abort_flag) break;
-        const uint32_t b = j & 1;
+        const int j = t0 + jl;
+        const uint32_t b = jl & 1;
         const uint32_t n = b ? use1 : use0;
-        const uint32_t ws = (tile0 + j) % WSLOTS, wn = (tile0 + j) / WSLOTS;
+        const uint32_t ws = (tbase + jl) % WSLOTS, wn = (tbase + jl) / WSLOTS;
         pc.start();
         if (!mbar_wait_bounded(&sh->acc_full[b], n & 1u)) { sh->abort_flag = 1; break; }
         pc.stop(1);
@@ -376,7 +390,8 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         if (b) ++use1; else ++use0;
       }
-      if (active) p.list_cnt[lrow * 2 + strm] = overflowed ? p.caph + 1 : static_cast<int>(wp - buf);
+      if (active) p.list_cnt[seg] = overflowed ? p.caph + 1 : static_cast<int>(wp - buf);
+      tbase += nt;
       if (sh->abort_flag) break;
     }
     if (lane == 0) pc.flush(warp);
@@ -409,6 +424,23 @@ struct IdxOutSink {
   }
 };
 
+// flat view of a row's list segments for the general selection (rare path: the segment is found by a short scan)
+struct SegListSrc {
+  const uint2* base;
+  const int* cnt;
+  int cap;
+  int nseg;
+  __device__ __forceinline__ unsigned long long operator()(int i) const {
+    int sgm = 0;
+    while (sgm + 1 < nseg && i >= cnt[sgm]) {
+      i -= cnt[sgm];
+      ++sgm;
+    }
+    const uint2 e = base[static_cast<size_t>(sgm) * cap + i];
+    return composite(score_key(__uint_as_float(e.x)), e.y);
+  }
+};
+
 __global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const IdxParams p) {
   __shared__ TightSmem tsm[FIN_WARPS];
   __shared__ SelectSmem<SEL_BINS> gsm;  // general routine, used by one warp at a time (rare fall-back)
@@ -419,10 +451,18 @@ __global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const Id
   const int row = p.row_begin + blockIdx.x * FIN_WARPS + w;
   if (row >= p.row_end || row >= p.T) return;
   const size_t lrow = static_cast<size_t>(row - p.row_begin);
-  const int n0 = p.list_cnt[lrow * 2], n1 = p.list_cnt[lrow * 2 + 1];
-  if (n0 > p.caph || n1 > p.caph || n0 + n1 < p.k) {  // overflowed, or tau was too high: redo from -inf
+  const int nseg = 2 * p.nsplit;
+  const int* cnt = p.list_cnt + lrow * nseg;
+  int n = 0;
+  bool over = false;
+  for (int sgm = 0; sgm < nseg; ++sgm) {
+    const int c = cnt[sgm];
+    over = over || c > p.caph;
+    n += c;
+  }
+  if (over || n < p.k) {  // a list overflowed, or tau was too high: redo from -inf
     if (lane == 0) {
-      atomicAdd(&g_fin_stats[(n0 > p.caph || n1 > p.caph) ? 0 : 1], 1ull);
+      atomicAdd(&g_fin_stats[over ? 0 : 1], 1ull);
       p.tau_redo[row] = -INFINITY;
       p.block_flags[row / BM] = 1;
     }
@@ -430,13 +470,13 @@ __global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const Id
   }
   if (lane == 0) p.tau_redo[row] = INFINITY;
   if (p.debug & 1) return;
-  const uint2* b0 = p.cand + lrow * 2 * p.caph;
+  const uint2* b0 = p.cand + lrow * nseg * p.caph;
   IdxOutSink sink{p.out_idx + static_cast<int64_t>(row) * p.k,
                   p.out_scores ? static_cast<unsigned char*>(p.out_scores) +
                                      static_cast<int64_t>(row) * p.k * (p.out_dtype == GW_F32 ? 4 : 2)
                                : nullptr,
                   p.out_dtype};
-  TightLists L{b0, n0, b0 + p.caph, n1};
+  TightLists L{b0, cnt, p.caph, nseg};
   const uint32_t lo = score_key(p.tau_in[row]), hi = score_key(p.smax_in[row]);
   if (warp_select_tight(L, p.k, lo, hi, tsm[w], lane, sink, nullptr) == p.k) {
     if (lane == 0) atomicAdd(&g_fin_stats[3], 1ull);
@@ -454,11 +494,11 @@ __global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const Id
     report_status(p.status, GW_ERR_TIMEOUT);
     return;
   }
-  TwoSegSrc src{b0, b0 + p.caph, n0};
+  SegListSrc src{b0, cnt, p.caph, nseg};
   FinalSink fsink{sink.oi, sink.os, sink.dtype};
-  group_select_topk<32, SEL_BINS, TwoSegSrc, FinalSink, 8>(src, n0 + n1, p.k, static_cast<unsigned long long>(lo) << 32,
-                                                           (static_cast<unsigned long long>(hi) << 32) | 0xffffffffull, gsm, lane, 0,
-                                                           fsink, nullptr, true);
+  group_select_topk<32, SEL_BINS, SegListSrc, FinalSink, 8>(src, n, p.k, static_cast<unsigned long long>(lo) << 32,
+                                                            (static_cast<unsigned long long>(hi) << 32) | 0xffffffffull, gsm, lane, 0,
+                                                            fsink, nullptr, true);
   __threadfence_block();
   if (lane == 0) atomicExch(&gsm_lock, 0);
 }

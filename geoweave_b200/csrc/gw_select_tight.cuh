@@ -26,22 +26,24 @@ __device__ __forceinline__ uint32_t ts_bin(uint32_t key, uint32_t lo, int shift)
   return d < TS_BINS - 1 ? d : TS_BINS - 1;
 }
 
-// Sources are split in two segments.  A source provides count(seg), bits(seg, i) and entry(seg, i).
-// Two contiguous arrays of (score bits, index):
+// Sources come in segments.  A source provides segments(), count(seg), bits(seg, i) and entry(seg, i).
+// nseg arrays of (score bits, index), `cap` entries apart, with their lengths in cnt[0..nseg):
 struct TightLists {
-  const uint2* __restrict__ a;
-  int na;
-  const uint2* __restrict__ b;
-  int nb;
-  __device__ __forceinline__ int count(int seg) const { return seg ? nb : na; }
-  __device__ __forceinline__ uint32_t bits(int seg, int i) const { return (seg ? b : a)[i].x; }
-  __device__ __forceinline__ uint2 entry(int seg, int i) const { return (seg ? b : a)[i]; }
+  const uint2* __restrict__ base;
+  const int* __restrict__ cnt;
+  int cap;
+  int nseg;
+  __device__ __forceinline__ int segments() const { return nseg; }
+  __device__ __forceinline__ int count(int seg) const { return cnt[seg]; }
+  __device__ __forceinline__ uint32_t bits(int seg, int i) const { return base[static_cast<size_t>(seg) * cap + i].x; }
+  __device__ __forceinline__ uint2 entry(int seg, int i) const { return base[static_cast<size_t>(seg) * cap + i]; }
 };
 // One dense row of fp32 scores, index = column:
 struct TightDenseRow {
   const float* __restrict__ row;
   int n;
-  __device__ __forceinline__ int count(int seg) const { return seg ? 0 : n; }
+  __device__ __forceinline__ int segments() const { return 1; }
+  __device__ __forceinline__ int count(int) const { return n; }
   __device__ __forceinline__ uint32_t bits(int, int i) const { return __float_as_uint(row[i]); }
   __device__ __forceinline__ uint2 entry(int, int i) const { return make_uint2(__float_as_uint(row[i]), static_cast<uint32_t>(i)); }
 };
@@ -67,7 +69,7 @@ __device__ int warp_select_tight(const Lists& L, int k, uint32_t lo, uint32_t hi
     __syncwarp();
     // ---- histogram of the undecided keys ----
 #pragma unroll 1
-    for (int seg = 0; seg < 2; ++seg) {
+    for (int seg = 0; seg < L.segments(); ++seg) {
       const int n = L.count(seg);
       for (int base = lane; base < n; base += 32 * TS_U) {
         uint32_t sb[TS_U];
@@ -139,7 +141,7 @@ __device__ int warp_select_tight(const Lists& L, int k, uint32_t lo, uint32_t hi
   // ---- output pass: emit everything above the boundary range, stash the boundary range ----
   int out_n = 0, side_n = 0;
 #pragma unroll 1
-  for (int seg = 0; seg < 2; ++seg) {
+  for (int seg = 0; seg < L.segments(); ++seg) {
     const int n = L.count(seg);
     for (int base0 = 0; base0 < n; base0 += 32 * TS_U) {
       uint2 e[TS_U];
