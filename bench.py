@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers per step (profiling)")
     ap.add_argument("--profile", action="store_true", help="profiling run: exact --warmup, no e2e pass, no CPU arm")
+    ap.add_argument("--micro", action="store_true",
+                    help="instead of the path, time the stand-alone operators (exact top-k of materialised scores, merge of "
+                         "two lists, scalar attention kernels) and print one JSON line with their roofline fractions")
     return ap.parse_args()
 
 
@@ -161,7 +164,7 @@ def run_ours(args):
     from geoweave_b200 import _lib
     from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
     from geoweave_b200.custom_indexer import sparse_topk_indexer_inference_func
-    from geoweave_b200.sharding import gather_rows, row_partition
+    from geoweave_b200.sharding import gather_rows, gather_rows_async, row_partition
 
     _lib.load()  # fail loudly if the CUDA library is missing: there is no other path
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -200,8 +203,9 @@ def run_ours(args):
     stage_events = []  # (start, after indexer, after attention) per layer call, only while timing
 
     def layer_op(t, record):
-        if world > 1:
-            k_idx, w, k, v = [gather_rows(t[n], n_tokens) for n in ("k_idx", "w", "k", "v")]
+        if world > 1:  # the indexer needs K_idx and w; K and V are gathered behind it
+            k_idx, w = gather_rows(t["k_idx"], n_tokens), gather_rows(t["w"], n_tokens)
+            k_pend, v_pend = gather_rows_async(t["k"], n_tokens), gather_rows_async(t["v"], n_tokens)
         else:
             k_idx, w, k, v = t["k_idx"], t["w"], t["k"], t["v"]
         if record:
@@ -210,6 +214,8 @@ def run_ours(args):
         idx, _ = sparse_topk_indexer_inference_func(t["q_idx"], k_idx, w, None, TOPK, DI ** -0.5, 0, 0, return_scores=False)
         if record:
             e1.record()
+        if world > 1:
+            k, v = k_pend.result(), v_pend.result()
         out, _ = sparse_index_flash_attn_inference_func(t["q"], k, v, idx, None, False, D ** -0.5, False)
         if record:
             e2.record()
@@ -328,8 +334,79 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_micro(args):
+    """Stand-alone operators of the drop-in API that the fused path does not go through."""
+    import geoweave_b200
+    from geoweave_b200 import _lib
+    from geoweave_b200.custom_flash_attn.sparse_index_flash_attn import sparse_attention_forward
+    from geoweave_b200.custom_indexer.merge_two_topk_cuda import merge_two_topk_inplace
+    from geoweave_b200.custom_indexer.topk_exact_cuda import topk_exact_select
+
+    _lib.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    try:
+        hbm_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        hbm_peak = 6650.0
+    g = torch.Generator(device="cpu").manual_seed(3)
+
+    def timed(fn, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    out = []
+    rows, cols, k = 8192, 33312, 1024  # 1.09 GB of fp32 scores: larger than L2
+    sc = torch.randn(1, rows, cols, device=dev)
+    o_s = torch.empty(1, rows, k, device=dev)
+    o_p = torch.empty(1, rows, k, dtype=torch.int32, device=dev)
+    ms = timed(lambda: topk_exact_select(sc, o_s, o_p))
+    nbytes = 4 * rows * cols + 8 * rows * k
+    out.append({"op": "topk_exact_select", "shape": [rows, cols, k], "ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6,
+                "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
+    del sc
+    rows = 33312
+    a_s = torch.randn(1, rows, k, device=dev)
+    b_s = torch.randn(1, rows, k, device=dev)
+    a_i = torch.randint(0, 30000, (1, rows, k), device=dev, dtype=torch.int32)
+    b_p = torch.randint(0, 3000, (1, rows, k), device=dev, dtype=torch.int64)
+    m_s, m_i = torch.empty_like(a_s), torch.empty_like(a_i)
+    ms = timed(lambda: merge_two_topk_inplace(a_s, a_i, b_s, b_p, 30000, m_s, m_i))
+    nbytes = rows * k * (4 + 4 + 4 + 8 + 4 + 4)
+    out.append({"op": "merge_two_topk_inplace", "shape": [rows, k], "ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6,
+                "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
+    T, S = 4096, 33312
+    for dtype, name in ((torch.float32, "sparse attention, scalar kernel, fp32"), (torch.bfloat16, "sparse attention, scalar kernel, bf16 head-major")):
+        q = torch.randn(1, T, H, D, device=dev).to(dtype)
+        kk = torch.randn(1, S, H, D, device=dev).to(dtype)
+        vv = torch.randn(1, S, H, D, device=dev).to(dtype)
+        pos = torch.randint(0, S, (1, T, TOPK), device=dev, dtype=torch.int32)
+        if dtype == torch.bfloat16:  # [B,H,T,D] inputs are gathered head by head by the scalar kernel
+            q, kk, vv = [x.transpose(1, 2).contiguous() for x in (q, kk, vv)]
+            ms = timed(lambda: sparse_attention_forward(q, kk, vv, pos, None, False, False, "bhtd"))
+        else:
+            ms = timed(lambda: sparse_attention_forward(q, kk, vv, pos, None, False, False, "bthd"))
+        es = q.element_size()
+        nbytes = T * (TOPK * 2 * H * D * es + TOPK * 4 + 2 * H * D * es)
+        out.append({"op": name, "shape": [T, S, TOPK], "ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak,
+                    "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
+    geoweave_b200.check_status()
+    print(json.dumps({"micro": out}), flush=True)
+
+
 def main():
     args = parse()
+    if args.micro:
+        run_micro(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -16,11 +16,9 @@
 // the last tile the two streams' lists of a row are merged by one more exact selection, which writes the
 // result.  The N x N score matrix never exists in memory.
 //
-// tau starts from a sampled estimate when the key set is large: scores against every `step`-th key are
-// written densely by the same main loop (score mode), a small kernel takes their r-th largest per row, r
-// chosen so that about 2k keys pass.  The estimate is only a filter: a row that ends with fewer than k
-// candidates is redone from tau = -inf by a second launch that normally finds an empty work list, so the
-// result is exact whatever the data.
+// This is the robust form: it is exact from tau = -inf whatever the data and is used for small key sets, for the
+// dense score mode (verification, and the sampled pass that seeds the thresholds of the fast form in
+// gw_indexer_fast.cuh) and to redo the row blocks the fast form flags.
 #include <cuda.h>
 #include <math.h>
 #include <stdlib.h>
@@ -368,45 +366,6 @@ __global__ void prep_w_kernel(const T* w, int S, int Hi, float scale, float4* ws
   if (s < S)
     for (int h = 0; h < Hi; ++h) v[h] = to_float(w[static_cast<size_t>(s) * Hi + h]) * scale;
   wsc[s] = make_float4(v[0], v[1], v[2], v[3]);
-}
-
-// r-th largest of each dense row -> tau (one warp per row)
-struct DenseF32Src {
-  const float* row;
-  __device__ __forceinline__ unsigned long long operator()(int i) const {
-    return composite(score_key(row[i]), static_cast<uint32_t>(i));
-  }
-};
-struct NullSink {
-  __device__ __forceinline__ void operator()(int, unsigned long long) const {}
-};
-constexpr int KTH_WARPS = 8;
-__global__ void __launch_bounds__(KTH_WARPS * 32) kth_rows_kernel(const float* sc, int m, int64_t stride, int T, int r,
-                                                                  float* tau, float* smax) {
-  __shared__ SelectSmem<SEL_BINS> sm[KTH_WARPS];
-  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * KTH_WARPS + w;
-  if (row >= T) return;
-  DenseF32Src src{sc + static_cast<int64_t>(row) * stride};
-  uint32_t kmin = 0xffffffffu, kmax = 0u;
-  for (int i = lane; i < m; i += 32) {
-    const uint32_t key = score_key(src.row[i]);
-    kmin = min(kmin, key);
-    kmax = max(kmax, key);
-  }
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) {
-    kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, d));
-    kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, d));
-  }
-  unsigned long long kth = 0;
-  group_select_topk<32, SEL_BINS>(src, m, r, static_cast<unsigned long long>(kmin) << 32,
-                                  (static_cast<unsigned long long>(kmax) << 32) | 0xffffffffull, sm[w], lane, 0,
-                                  NullSink{}, &kth);
-  if (lane == 0) {
-    tau[row] = key_score(composite_key(kth));
-    smax[row] = key_score(kmax);
-  }
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -11,7 +11,7 @@ from typing import List, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["row_partition", "shard_rows", "gather_rows", "sparse_global_attention_sharded"]
+__all__ = ["row_partition", "shard_rows", "gather_rows", "gather_rows_async", "sparse_global_attention_sharded"]
 
 
 def row_partition(n_rows: int, world_size: int) -> List[Tuple[int, int]]:
@@ -32,7 +32,31 @@ def shard_rows(x: torch.Tensor, rank: int, world_size: int, dim: int = 1) -> tor
     return x.narrow(dim, lo, hi - lo)
 
 
+class _PendingGather:
+    """Handle of an all-gather in flight; ``result()`` waits for it and returns the full tensor."""
+
+    def __init__(self, work, finish):
+        self._work, self._finish, self._out = work, finish, None
+
+    def result(self) -> torch.Tensor:
+        if self._out is None:
+            if self._work is not None:
+                self._work.wait()
+            self._out = self._finish()
+        return self._out
+
+
+def gather_rows_async(x: torch.Tensor, n_rows: int, group=None, dim: int = 1) -> _PendingGather:
+    """``gather_rows`` that returns at once: the collective runs on the communication stream while the caller
+    launches independent kernels (the indexer needs only K_idx and w; K and V can arrive behind it)."""
+    return _gather_rows(x, n_rows, group, dim, True)
+
+
 def gather_rows(x: torch.Tensor, n_rows: int, group=None, dim: int = 1) -> torch.Tensor:
+    return _gather_rows(x, n_rows, group, dim, False).result()
+
+
+def _gather_rows(x: torch.Tensor, n_rows: int, group, dim: int, async_op: bool) -> _PendingGather:
     """All-gather row shards (``row_partition`` sizes along ``dim``) into the full ``n_rows`` tensor.
 
     Equal shards go through one ``all_gather_into_tensor``; ragged shards are padded to the largest and
@@ -46,7 +70,7 @@ def gather_rows(x: torch.Tensor, n_rows: int, group=None, dim: int = 1) -> torch
     if x.shape[dim] != hi - lo:
         raise ValueError(f"rank {rank}: shard has {x.shape[dim]} rows, partition of {n_rows} over {world} expects {hi - lo}")
     if world == 1:
-        return x
+        return _PendingGather(None, lambda: x)
     xm = x.movedim(dim, 0).contiguous()
     biggest = max(b - a for a, b in parts)
     if xm.shape[0] < biggest:
@@ -54,13 +78,18 @@ def gather_rows(x: torch.Tensor, n_rows: int, group=None, dim: int = 1) -> torch
         xm = torch.cat([xm, pad], 0)
     out = torch.empty((world * biggest,) + tuple(xm.shape[1:]), dtype=xm.dtype, device=xm.device)
     if xm.is_cuda:
-        dist.all_gather_into_tensor(out, xm, group=group)
+        work = dist.all_gather_into_tensor(out, xm, group=group, async_op=async_op)
     else:  # gloo (CPU tests)
         chunks = list(out.chunk(world, 0))
-        dist.all_gather(chunks, xm, group=group)
-    if any(b - a != biggest for a, b in parts):
-        out = torch.cat([out[r * biggest: r * biggest + (b - a)] for r, (a, b) in enumerate(parts)], 0)
-    return out.movedim(0, dim)
+        work = dist.all_gather(chunks, xm, group=group, async_op=async_op)
+
+    def finish():
+        full = out
+        if any(b - a != biggest for a, b in parts):
+            full = torch.cat([out[r * biggest: r * biggest + (b - a)] for r, (a, b) in enumerate(parts)], 0)
+        return full.movedim(0, dim)
+
+    return _PendingGather(work if async_op else None, finish)
 
 
 def sparse_global_attention_sharded(q_idx, k_idx, w, q, k, v, topk: int, n_tokens: int, group=None,
@@ -84,8 +113,8 @@ def sparse_global_attention_sharded(q_idx, k_idx, w, q, k, v, topk: int, n_token
         indexer, attention = ops
     k_idx_full = gather_rows(k_idx, n_tokens, group)
     w_full = gather_rows(w, n_tokens, group)
-    k_full = gather_rows(k, n_tokens, group)
-    v_full = gather_rows(v, n_tokens, group)
+    k_pending = gather_rows_async(k, n_tokens, group)  # K and V arrive while the indexer runs
+    v_pending = gather_rows_async(v, n_tokens, group)
     idx = indexer(q_idx, k_idx_full, w_full, topk, idx_scale)
-    out = attention(q, k_full, v_full, idx, attn_scale)
+    out = attention(q, k_pending.result(), v_pending.result(), idx, attn_scale)
     return out, idx
