@@ -236,3 +236,28 @@ def test_long_key_set_few_queries():
     geoweave_b200.check_status()
     res = orc.audit_topk(idx, orc.indexer_scores(q, kx, w, 0.125), 1024, q, kx, w, 0.125)
     assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
+
+
+@pytest.mark.parametrize("Hi,dtype", [(1, torch.bfloat16), (2, torch.float16), (3, torch.bfloat16), (4, torch.float16)])
+def test_fast_path_other_head_counts_and_fp16(Hi, dtype):
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    q, kx, w = make_indexer_inputs(150, 8328, Hi=Hi, seed=40 + Hi, dtype=dtype, integer=True)
+    _finalize_counters()
+    idx, sc = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, 256, 0.125, 256)
+    geoweave_b200.check_status()
+    assert sum(_finalize_counters()) == 150  # went through the fast path's finalize kernel
+    scores = orc.indexer_scores(q, kx, w, 0.125)
+    assert torch.equal(sorted_idx(idx), orc.topk_tie_exact(scores, 256).long())
+    assert torch.equal(sc.float().cpu(), scores.gather(-1, idx.long().cpu()).to(dtype).float())
+
+
+def test_batch_of_two_on_the_fast_path():
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    qa, ka, wa = make_indexer_inputs(140, 8328, seed=51, integer=True)
+    qb, kb, wb = make_indexer_inputs(140, 8328, seed=52, integer=True)
+    q, kx, w = torch.cat([qa, qb]), torch.cat([ka, kb]), torch.cat([wa, wb])
+    idx, _ = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, 300, 0.125, 256)
+    geoweave_b200.check_status()
+    assert torch.equal(sorted_idx(idx), orc.topk_tie_exact(orc.indexer_scores(q, kx, w, 0.125), 300).long())
