@@ -43,6 +43,25 @@ def test_topk_exact_sweep(cols, k, kind):
     assert torch.equal(sorted_idx(pos), orc.topk_tie_exact(sc, k).long())
 
 
+@pytest.mark.parametrize("cols,k,rows", [(8328, 256, 1300), (8329, 512, 40), (33312, 1024, 300), (40001, 64, 10), (60000, 1024, 5)])
+@pytest.mark.parametrize("kind", ["heavy_tail", "narrow", "mostly_zero"])
+def test_topk_exact_many_rows_and_awkward_distributions(cols, k, rows, kind):
+    """Rows in shared memory (CTAs walk several rows; odd widths take plain loads; 60000 columns do not fit and go
+    to the re-reading kernel), with score distributions that defeat a sampled threshold or crowd the boundary."""
+    from geoweave_b200.custom_indexer.topk_exact_cuda import topk_exact_select
+
+    g = torch.Generator().manual_seed(cols * 3 + k)
+    if kind == "heavy_tail":
+        sc = torch.exp(3.0 * torch.randn(1, rows, cols, generator=g)) * torch.sign(torch.randn(1, rows, cols, generator=g))
+    elif kind == "narrow":
+        sc = 1.0 + torch.randint(0, 4096, (1, rows, cols), generator=g).float() * 2.0 ** -20
+    else:
+        sc = torch.relu(torch.randn(1, rows, cols, generator=g) - 2.2)  # about 1.4 % of the columns are positive
+    vals, pos = topk_exact_select(sc.to(dev()), k=k)
+    assert torch.equal(sorted_idx(pos), orc.topk_tie_exact(sc, k).long())
+    assert torch.equal(vals.cpu(), sc.gather(-1, pos.cpu()))
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_topk_exact_16bit_scores(dtype):
     from geoweave_b200.custom_indexer.topk_exact_cuda import topk_exact_select
