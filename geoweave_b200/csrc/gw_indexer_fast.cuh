@@ -63,12 +63,6 @@ struct alignas(8) FastShared {
   volatile int abort_flag;
 };
 
-#ifdef GW_FAST_NO_APPEND
-constexpr bool kFastNoAppend = true;
-#else
-constexpr bool kFastNoAppend = false;
-#endif
-
 // packed fp32 pairs (sm_100 f32x2 pipe): d = a * b + c on both halves
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
   float2 d;
@@ -97,23 +91,13 @@ __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
 template <int HI>
 __device__ __forceinline__ void fast_load_chunk(uint32_t taddr, uint32_t (&a)[HI][8]) {
 #pragma unroll
-#ifdef GW_NO_TMEM_LD  // timing experiment: arithmetic on whatever the registers hold
-  for (int h = 0; h < HI; ++h)
-#pragma unroll
-    for (int c = 0; c < 8; ++c) asm volatile("xor.b32 %0, %0, %1;" : "+r"(a[h][c]) : "r"(taddr));
-#else
   for (int h = 0; h < HI; ++h) tmem_ld_x8(taddr + h * FBN, a[h]);
-#endif
 }
 
 // Append (score, col) at *wp and advance wp when score >= tau (and col < S if GUARD): compare, predicated store and
 // predicated pointer bump in one block, so an append costs four instructions and never a branch.
 template <bool GUARD>
 __device__ __forceinline__ void append_if(uint2*& wp, float s, float tau, uint32_t col, int S) {
-#ifdef GW_FAST_SUM  // timing experiment: keep the arithmetic alive without any store
-  wp = reinterpret_cast<uint2*>(reinterpret_cast<unsigned long long>(wp) + __float_as_uint(s));
-  return;
-#endif
   if (GUARD) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -124,15 +108,6 @@ __device__ __forceinline__ void append_if(uint2*& wp, float s, float tau, uint32
         : "+l"(wp)
         : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col), "r"(S));
   } else {
-#ifdef GW_APPEND_IMAD  // experiment: pointer bump as one wide multiply-add on the FMA pipe
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ge.f32 p, %1, %2;\n\t"
-        "@p st.global.v2.b32 [%0], {%3, %4};\n\t"
-        "@p mad.wide.u32 %0, %5, %6, %0;\n\t}"
-        : "+l"(wp)
-        : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col), "r"(8u), "r"(1u));
-#else
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ge.f32 p, %1, %2;\n\t"
@@ -140,7 +115,6 @@ __device__ __forceinline__ void append_if(uint2*& wp, float s, float tau, uint32
         "@p add.u64 %0, %0, 8;\n\t}"
         : "+l"(wp)
         : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col));
-#endif
   }
 }
 
@@ -153,12 +127,8 @@ __device__ __forceinline__ void fast_reduce_chunk(const uint32_t (&a)[HI][8], co
   float2 acc[4];
 #pragma unroll
   for (int h = 0; h < HI; ++h) {
-#ifdef GW_W_CONST  // timing experiment: no shared-memory reads of the weights
-    const float4 wa = make_float4(0.1f * h, 0.2f, 0.3f, 0.4f), wb = make_float4(0.5f, 0.6f, 0.7f, 0.8f + c0);
-#else
     const float4 wa = *reinterpret_cast<const float4*>(wt + h * FBN + c0);
     const float4 wb = *reinterpret_cast<const float4*>(wt + h * FBN + c0 + 4);
-#endif
     float r[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
@@ -170,19 +140,14 @@ __device__ __forceinline__ void fast_reduce_chunk(const uint32_t (&a)[HI][8], co
     const float2 w2[4] = {make_float2(wa.x, wa.y), make_float2(wa.z, wa.w), make_float2(wb.x, wb.y), make_float2(wb.z, wb.w)};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-#ifdef GW_FAST_SCALAR
-      acc[q].x = (h == 0) ? r[2 * q] * w2[q].x : fmaf(r[2 * q], w2[q].x, acc[q].x);
-      acc[q].y = (h == 0) ? r[2 * q + 1] * w2[q].y : fmaf(r[2 * q + 1], w2[q].y, acc[q].y);
-#else
       const float2 r2 = make_float2(r[2 * q], r[2 * q + 1]);
       acc[q] = (h == 0) ? fmul2(r2, w2[q]) : ffma2(r2, w2[q], acc[q]);
-#endif
     }
   }
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     const float s = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-    if (!kFastNoAppend) append_if<GUARD>(wp, s, tau, static_cast<uint32_t>(col_g + c), S);
+    append_if<GUARD>(wp, s, tau, static_cast<uint32_t>(col_g + c), S);
   }
 }
 
