@@ -4,6 +4,7 @@
 
 #include "gw_common.cuh"
 #include "gw_select.cuh"
+#include "gw_select_tight.cuh"
 
 namespace gw {
 
@@ -560,17 +561,79 @@ struct ListSink {
   }
 };
 
+// the two lists as segments of (score bits, index) for the lean warp routine; an empty slot (negative index)
+// becomes (-inf, 0xffffffff), which loses every comparison and is written back as index -1
+template <typename T>
+struct TwoListSegs {
+  const T* a_s;
+  const int32_t* a_i;
+  const T* b_s;
+  const int64_t* b_p;
+  int ka, kb;
+  int64_t b_start;
+  __device__ __forceinline__ int segments() const { return 2; }
+  __device__ __forceinline__ int count(int seg) const { return seg == 0 ? ka : kb; }
+  __device__ __forceinline__ uint2 entry(int seg, int i) const {
+    float s;
+    int64_t idx;
+    if (seg == 0) {
+      s = to_float(a_s[i]);
+      idx = a_i[i];
+    } else {
+      s = to_float(b_s[i]);
+      idx = b_p[i];
+      idx = idx < 0 ? idx : idx + b_start;
+    }
+    return idx < 0 ? make_uint2(0xff800000u, 0xffffffffu) : make_uint2(__float_as_uint(s), static_cast<uint32_t>(idx));
+  }
+  __device__ __forceinline__ uint32_t bits(int seg, int i) const { return entry(seg, i).x; }
+};
+template <typename T>
+struct ListBitsSink {
+  T* os;
+  int32_t* oi;
+  __device__ __forceinline__ void operator()(int pos, uint32_t bits, uint32_t idx) const {
+    oi[pos] = static_cast<int32_t>(idx);
+    os[pos] = from_float<T>(__uint_as_float(bits));
+  }
+};
+
+struct MergeSmem {
+  union {
+    SelectSmem<kMergeBins> gen;
+    TightSmem tight;
+  };
+};
+
+// The lean warp routine first (32-bit keys, about two dozen instructions per entry); a boundary crowded with
+// equal scores, or fewer than k entries in all, goes to the general routine.  Both may write over list a: an
+// output position is never ahead of the entries already read into registers.
 template <typename T>
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_two_topk_kernel(const T* a_s, const int32_t* a_i, int ka,
                                                                           const T* b_s, const int64_t* b_p, int kb,
                                                                           int64_t b_start, int64_t rows, int k, T* os,
                                                                           int32_t* oi) {
-  __shared__ SelectSmem<kMergeBins> sm[kMergeWarps];
+  __shared__ MergeSmem sm[kMergeWarps];
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t r = static_cast<int64_t>(blockIdx.x) * kMergeWarps + w;
   if (r >= rows) return;
-  TwoListSrc<T> src{a_s + r * ka, a_i + r * ka, b_s + r * kb, b_p + r * kb, ka, b_start};
   const int n = ka + kb;
+  if (n > k) {
+    const TwoListSegs<T> segs{a_s + r * ka, a_i + r * ka, b_s + r * kb, b_p + r * kb, ka, kb, b_start};
+    uint32_t kmin = 0xffffffffu, kmax = 0u;
+    for (int seg = 0; seg < 2; ++seg)
+      for (int i = lane; i < segs.count(seg); i += 32) {
+        const uint32_t key = score_key(__uint_as_float(segs.bits(seg, i)));
+        kmin = min(kmin, key);
+        kmax = max(kmax, key);
+      }
+    kmin = __reduce_min_sync(0xffffffffu, kmin);
+    kmax = __reduce_max_sync(0xffffffffu, kmax);
+    const ListBitsSink<T> bsink{os + r * k, oi + r * k};
+    if (warp_select_tight(segs, k, kmin, kmax, sm[w].tight, lane, bsink, nullptr) == k) return;
+    __syncwarp();
+  }
+  TwoListSrc<T> src{a_s + r * ka, a_i + r * ka, b_s + r * kb, b_p + r * kb, ka, b_start};
   unsigned long long cmin = ~0ull, cmax = 0ull;
   for (int i = lane; i < n; i += 32) {
     const unsigned long long c = src(i);
@@ -585,7 +648,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_two_topk_kernel(const 
     cmax = b > cmax ? b : cmax;
   }
   ListSink<T> sink{os + r * k, oi + r * k};
-  const int got = group_select_topk<32, kMergeBins>(src, n, k, cmin, cmax, sm[w], lane, 0, sink, nullptr);
+  const int got = group_select_topk<32, kMergeBins>(src, n, k, cmin, cmax, sm[w].gen, lane, 0, sink, nullptr);
   for (int p = got + lane; p < k; p += 32) sink(p, 0ull);  // k > ka + kb: pad with empty slots
 }
 
