@@ -398,6 +398,17 @@ def run_micro(args):
         nbytes = T * (TOPK * 2 * H * D * es + TOPK * 4 + 2 * H * D * es)
         out.append({"op": name, "shape": [T, S, TOPK], "ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak,
                     "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
+    # the forward with and without attn_sum on the benchmark's own shape (bf16, token-major, every row a query)
+    T = S = 33312
+    q = torch.randn(1, T, H, D, device=dev).bfloat16()
+    kk = torch.randn(1, S, H, D, device=dev).bfloat16()
+    vv = torch.randn(1, S, H, D, device=dev).bfloat16()
+    pos = torch.randint(0, S, (1, T, TOPK), device=dev, dtype=torch.int32)
+    nbytes = T * (TOPK * 2 * H * D * 2 + TOPK * 4 + 2 * H * D * 2)
+    for with_sum, name in ((False, "sparse attention, tensor-core kernel, bf16"), (True, "sparse attention + attn_sum, tensor-core kernel, bf16")):
+        ms = timed(lambda: sparse_attention_forward(q, kk, vv, pos, None, with_sum, with_sum, "bthd"), reps=3)
+        out.append({"op": name, "shape": [T, S, TOPK], "ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak,
+                    "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
     geoweave_b200.check_status()
     print(json.dumps({"micro": out}), flush=True)
 

@@ -389,14 +389,22 @@ extern "C" int gw_sparse_attn_fwd(const void* q, const void* k, const void* v, c
   const bool use_mma = dtype != GW_F32 && D == 64 && (H == 8 || H == 16) && p.kv_heads_contiguous &&
                        !(force_scalar && force_scalar[0] == '1');
   int rc;
+  bool sum_done = false;
   if (use_mma) {
-    if (dtype == GW_BF16) rc = (H == 16) ? launch_attn_mma<__nv_bfloat16, 2>(p, st) : launch_attn_mma<__nv_bfloat16, 1>(p, st);
-    else rc = (H == 16) ? launch_attn_mma<__half, 2>(p, st) : launch_attn_mma<__half, 1>(p, st);
+    // attn_sum comes out of the same kernel when the query's logits fit its shared-memory buffer
+    sum_done = attn_sum != nullptr && K <= AM_SUM_MAXK;
+    if (sum_done) {
+      if (dtype == GW_BF16) rc = (H == 16) ? launch_attn_mma<__nv_bfloat16, 2, true>(p, st) : launch_attn_mma<__nv_bfloat16, 1, true>(p, st);
+      else rc = (H == 16) ? launch_attn_mma<__half, 2, true>(p, st) : launch_attn_mma<__half, 1, true>(p, st);
+    } else {
+      if (dtype == GW_BF16) rc = (H == 16) ? launch_attn_mma<__nv_bfloat16, 2, false>(p, st) : launch_attn_mma<__nv_bfloat16, 1, false>(p, st);
+      else rc = (H == 16) ? launch_attn_mma<__half, 2, false>(p, st) : launch_attn_mma<__half, 1, false>(p, st);
+    }
   } else {
     rc = dispatch_t<0>(p, dtype, D, G, st);
   }
   if (rc != GW_OK) return rc;
-  if (attn_sum != nullptr) {
+  if (attn_sum != nullptr && !sum_done) {
     if (H / G > 1) GW_CUDA_TRY(cudaMemsetAsync(attn_sum, 0, sizeof(float) * static_cast<size_t>(B) * T * K, st));
     rc = dispatch_t<1>(p, dtype, D, G, st);
   }

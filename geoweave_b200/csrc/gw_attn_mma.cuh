@@ -14,6 +14,12 @@
 // V row, rows padded by 16 bytes so that ldmatrix hits eight different bank groups), three batches in flight,
 // one full/empty mbarrier pair per batch slot, and the stream of batches runs on across queries without a
 // bubble.  Padding entries of the index list are replaced by key 0 in the gather and masked in the softmax.
+//
+// SUM variant (attn_sum[t, j] = sum over heads of the softmax weight of key j, fp32): two batch slots instead of
+// three, and the space of the third holds the scaled logits of the current query, [head][key] fp32 (K <= 1024).
+// When a query's keys are through, the compute warps meet on an mbarrier, every thread sums
+// exp2(logit - m_h) / l_h over the heads for its keys and writes them, and a second mbarrier hands the buffer to
+// the next query -- K is gathered once, not twice as with a separate pass.
 #pragma once
 
 namespace gw {
@@ -25,6 +31,8 @@ constexpr int AM_PROD = 4;           // producer warps: one warp alone cannot is
 constexpr int AM_THREADS = (AM_WARPS + AM_PROD) * 32;
 constexpr int AM_BATCH = 16;         // keys per batch (the M of the score MMA, the K of the output MMA)
 constexpr int AM_NB = 3;             // batch slots
+constexpr int AM_NB_SUM = 2;         // batch slots of the variant that also produces attn_sum
+constexpr int AM_SUM_MAXK = 1024;    // keys per query the variant's logit buffer holds
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -59,30 +67,36 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 struct AmShared {
   uint64_t full[AM_NB], empty[AM_NB];
+  uint64_t sum_ready, sum_done;   // SUM variant: logits and (m, 1/l) of a query complete / read by every warp
   uint32_t mask[AM_NB][AM_PROD];  // validity bits of each producer's four keys
+  float2 ml[AM_WARPS * 2];        // SUM variant: per head (reference maximum, 1 / denominator)
 };
 
 // HPW = heads per compute warp (H = 8 * HPW), D = 64
-template <typename T, int HPW>
+template <typename T, int HPW, bool SUM>
 __global__ void __launch_bounds__(AM_THREADS, 1) sparse_attn_mma_kernel(const AttnParams p) {
   constexpr int D = 64;
   constexpr int H = AM_WARPS * HPW;
+  constexpr int NB = SUM ? AM_NB_SUM : AM_NB;
   constexpr int ROW = H * D * 2;            // bytes of one K (or V) token row
   constexpr int RS = ROW + 16;              // row pitch in shared memory
   constexpr int TENS = AM_BATCH * RS;       // one tensor's rows of a batch
   constexpr int SLOT = 2 * TENS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  AmShared* sh = reinterpret_cast<AmShared*>(smem_raw + AM_NB * SLOT);
+  float* logits = reinterpret_cast<float*>(smem_raw + NB * SLOT);  // SUM: [H][AM_SUM_MAXK]
+  AmShared* sh = reinterpret_cast<AmShared*>(smem_raw + NB * SLOT + (SUM ? H * AM_SUM_MAXK * sizeof(float) : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int K = p.K;
   const int nbatch = (K + AM_BATCH - 1) / AM_BATCH;
   const long long nq = static_cast<long long>(p.B) * p.T;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < AM_NB; ++s) {
+    for (int s = 0; s < NB; ++s) {
       mbar_init(&sh->full[s], AM_PROD);
       mbar_init(&sh->empty[s], AM_WARPS);
     }
+    mbar_init(&sh->sum_ready, AM_WARPS);
+    mbar_init(&sh->sum_done, AM_WARPS);
     mbar_fence_init();
     fence_proxy_async_smem();
   }
@@ -106,8 +120,8 @@ __global__ void __launch_bounds__(AM_THREADS, 1) sparse_attn_mma_kernel(const At
         id_next = (bt + 1 < nbatch && kn < K) ? pos[kn] : -1;
         const bool valid = static_cast<uint32_t>(id) < S;
         const uint32_t mask = __ballot_sync(0xffffffffu, valid) & 0xfu;
-        const uint32_t slot = it % AM_NB;
-        if (!mbar_wait_bounded(&sh->empty[slot], ((it / AM_NB) & 1u) ^ 1u)) {
+        const uint32_t slot = it % NB;
+        if (!mbar_wait_bounded(&sh->empty[slot], ((it / NB) & 1u) ^ 1u)) {
           report_status(p.status, GW_ERR_TIMEOUT);
           return;
         }
@@ -132,9 +146,9 @@ __global__ void __launch_bounds__(AM_THREADS, 1) sparse_attn_mma_kernel(const At
   const uint32_t k_lane_off = static_cast<uint32_t>(((lane & 7) + 8 * ((lane >> 3) & 1)) * RS + (lane >> 4) * 16);
   const uint32_t v_lane_off = static_cast<uint32_t>(((lane & 7) + 8 * (lane >> 4)) * RS + ((lane >> 3) & 1) * 16);
   const uint32_t smem_base = smem_u32(smem_raw);
-  uint32_t it = 0;
+  uint32_t it = 0, qn = 0;
 
-  for (long long qi = blockIdx.x; qi < nq; qi += gridDim.x) {
+  for (long long qi = blockIdx.x; qi < nq; qi += gridDim.x, ++qn) {
     const int b = static_cast<int>(qi / p.T);
     const int t = static_cast<int>(qi % p.T);
     // B fragments of q: column 0 only, i.e. lanes 0..3 hold 32-bit words (two elements) of the q row
@@ -164,10 +178,16 @@ __global__ void __launch_bounds__(AM_THREADS, 1) sparse_attn_mma_kernel(const At
     }
 
     for (int bt = 0; bt < nbatch; ++bt, ++it) {
-      const uint32_t slot = it % AM_NB;
-      if (!mbar_wait_bounded(&sh->full[slot], (it / AM_NB) & 1u)) {
+      const uint32_t slot = it % NB;
+      if (!mbar_wait_bounded(&sh->full[slot], (it / NB) & 1u)) {
         report_status(p.status, GW_ERR_TIMEOUT);
         return;
+      }
+      if (SUM && bt == 0 && qn > 0) {  // the previous query's logits have been read by every warp
+        if (!mbar_wait_bounded(&sh->sum_done, (qn - 1) & 1u)) {
+          report_status(p.status, GW_ERR_TIMEOUT);
+          return;
+        }
       }
       const uint32_t mask = sh->mask[slot][0] | (sh->mask[slot][1] << 4) | (sh->mask[slot][2] << 8) | (sh->mask[slot][3] << 12);
       const uint32_t kaddr = smem_base + slot * SLOT + k_lane_off;
@@ -187,6 +207,10 @@ __global__ void __launch_bounds__(AM_THREADS, 1) sparse_attn_mma_kernel(const At
         // column 0 lives in the lanes with t4 == 0: s[0] = key g, s[2] = key g + 8 (log2 domain after scaling)
         float s0 = ok0 ? s[0] * p.scale_log2 : -INFINITY;
         float s1 = ok1 ? s[2] * p.scale_log2 : -INFINITY;
+        if (SUM && t4 == 0) {
+          logits[h * AM_SUM_MAXK + bt * AM_BATCH + g] = s0;
+          logits[h * AM_SUM_MAXK + bt * AM_BATCH + g + 8] = s1;
+        }
         float bmax = fmaxf(s0, s1);
         bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 4));
         bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 8));
@@ -200,7 +224,9 @@ __global__ void __launch_bounds__(AM_THREADS, 1) sparse_attn_mma_kernel(const At
             for (int r = 0; r < 4; ++r) acc[i][db][r] *= alpha;
           m_ref[i] = bmax;
         }
-        const float p0 = exp2f(s0 - m_ref[i]), p1 = exp2f(s1 - m_ref[i]);  // 0 for masked keys
+        // a masked key weighs nothing; written out because with nothing live yet m_ref is -inf and exp2f(-inf - -inf)
+        // would be NaN (a row, or its first batches, may be all padding)
+        const float p0 = ok0 ? exp2f(s0 - m_ref[i]) : 0.f, p1 = ok1 ? exp2f(s1 - m_ref[i]) : 0.f;
         if (t4 == 0) l_part[i] += p0 + p1;
         // ---- B fragment of p: lanes 0..3 need keys 2t,2t+1 (word 0) and 2t+8,2t+9 (word 1) ----
         const float pa = __shfl_sync(0xffffffffu, p0, 8 * t4);
@@ -229,6 +255,7 @@ __global__ void __launch_bounds__(AM_THREADS, 1) sparse_attn_mma_kernel(const At
       l += __shfl_xor_sync(0xffffffffu, l, 8);
       l += __shfl_xor_sync(0xffffffffu, l, 16);
       const float inv = l > 0.f ? 1.0f / l : 0.f;
+      if (SUM && lane == 0) sh->ml[h0 + i] = make_float2(l > 0.f ? m_ref[i] : 0.f, inv);
       if (t4 == 0) {
         T* op = static_cast<T*>(p.out) + b * p.os_b + static_cast<int64_t>(t) * p.os_t + static_cast<int64_t>(h0 + i) * p.os_h;
 #pragma unroll
@@ -241,14 +268,36 @@ __global__ void __launch_bounds__(AM_THREADS, 1) sparse_attn_mma_kernel(const At
               l > 0.f ? (m_ref[i] + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
     }
+    if (SUM) {
+      // ---- attn_sum of this query: all warps' logits and (m, 1/l) must be in; then keys are split over the threads ----
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->sum_ready);
+      if (!mbar_wait_bounded(&sh->sum_ready, qn & 1u)) {
+        report_status(p.status, GW_ERR_TIMEOUT);
+        return;
+      }
+      float* asum = p.attn_sum + qi * K;
+      for (int j = threadIdx.x; j < K; j += AM_WARPS * 32) {
+        float acc_j = 0.f;
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+          const float2 ml = sh->ml[h];
+          acc_j += exp2f(logits[h * AM_SUM_MAXK + j] - ml.x) * ml.y;  // a masked key holds -inf: contributes 0
+        }
+        asum[j] = acc_j;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->sum_done);
+    }
   }
 }
 
-template <typename T, int HPW>
+template <typename T, int HPW, bool SUM>
 int launch_attn_mma(const AttnParams& p, cudaStream_t st) {
   constexpr int H = AM_WARPS * HPW;
-  constexpr size_t SMEM = static_cast<size_t>(AM_NB) * 2 * AM_BATCH * (H * 64 * 2 + 16) + sizeof(AmShared);
-  auto kern = sparse_attn_mma_kernel<T, HPW>;
+  constexpr size_t SMEM = static_cast<size_t>(SUM ? AM_NB_SUM : AM_NB) * 2 * AM_BATCH * (H * 64 * 2 + 16) +
+                          (SUM ? static_cast<size_t>(H) * AM_SUM_MAXK * sizeof(float) : 0) + sizeof(AmShared);
+  auto kern = sparse_attn_mma_kernel<T, HPW, SUM>;
   GW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM)));
   int dev = 0, sms = 0;
   GW_CUDA_TRY(cudaGetDevice(&dev));

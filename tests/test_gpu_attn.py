@@ -100,3 +100,29 @@ def test_production_shape_bf16(T, S, K):
     o, _ = sparse_index_flash_attn_inference_func(q.to(dev()), k.to(dev()), v.to(dev()), idx.to(dev()), None, False, 0.125)
     o_ref, _, _ = orc.sparse_attention(q, k, v, idx, 0.125)
     assert (o.float().cpu() - o_ref).abs().max().item() <= BF16_TOL
+
+
+@pytest.mark.parametrize("T,S,K,H", [
+    (300, 4164, 1024, 16),    # logits of a query fit the kernel's buffer: attn_sum comes out of the forward kernel
+    (200, 4164, 1000, 8),     # K not a multiple of the batch of 16, eight heads
+    (150, 4164, 2048, 16),    # beyond the buffer: separate K-only pass
+    (4000, 2082, 512, 16),    # every CTA walks several queries: the buffer is handed from query to query
+])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_attn_sum_with_padding_at_production_shapes(T, S, K, H, dtype):
+    from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_func
+
+    g = torch.Generator().manual_seed(T + S + K + H)
+    q = torch.randn(1, T, H, 64, generator=g).to(dtype)
+    k = torch.randn(1, S, H, 64, generator=g).to(dtype)
+    v = torch.randn(1, S, H, 64, generator=g).to(dtype)
+    idx = torch.stack([torch.randperm(S, generator=g)[:K] for _ in range(T)]).view(1, T, K).to(torch.int32)
+    idx[0, 1::7, 5::3] = -1      # scattered padding
+    idx[0, 2, :] = -1            # a row of nothing but padding
+    idx[0, 3, 1:] = S + 3        # a single live key
+    o, asum = sparse_index_flash_attn_func(q.to(dev()), k.to(dev()), v.to(dev()), idx.to(dev()), None, False, 0.125)
+    o_ref, _, asum_ref = orc.sparse_attention(q, k, v, idx, 0.125)
+    assert (o.float().cpu() - o_ref).abs().max().item() <= BF16_TOL
+    assert asum.dtype == torch.float32 and asum.shape == (1, T, K)
+    assert (asum.cpu() - asum_ref).abs().max().item() <= 2e-3
+    assert torch.equal(asum[0, 2].cpu(), torch.zeros(K)) and abs(float(asum[0, 3, 0]) - H) <= 1e-3

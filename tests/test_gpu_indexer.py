@@ -299,3 +299,43 @@ def test_full_size_self_selection(N, k, ties, n_audit):
         assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, (N, c0, res)
         swapped += res["swapped"]
     assert swapped <= 0.02 * rows.numel() * k, swapped
+
+
+def test_indexer_and_attention_replay_from_a_cuda_graph():
+    """Both operators only enqueue on the caller's stream (no allocation, no synchronisation inside the C calls), so a
+    layer can be captured once and replayed on new contents of the same buffers."""
+    from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_inference_func
+
+    N, k = 8328, 256
+    g = torch.Generator().manual_seed(5)
+
+    def fresh():
+        qi, ki, w = make_indexer_inputs(N, N, seed=int(torch.randint(0, 1 << 30, (1,), generator=g)))
+        qkv = [torch.randn(1, N, 16, 64, generator=g).bfloat16() for _ in range(3)]
+        return [x.to(dev()) for x in (qi, ki, w, *qkv)]
+
+    def layer(qi, ki, w, q, kk, v):
+        idx, _ = sparse_topk_indexer_inference_func(qi, ki, w, None, k, 0.125, return_scores=False)
+        out, _ = sparse_index_flash_attn_inference_func(q, kk, v, idx, None, False, 0.125)
+        return idx, out
+
+    static = fresh()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer(*static)  # sizes the cached workspace outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        idx_g, out_g = layer(*static)
+    for _ in range(2):
+        new = fresh()
+        for dst, src in zip(static, new):
+            dst.copy_(src)
+        graph.replay()
+        torch.cuda.synchronize()
+        idx_e, out_e = layer(*new)
+        geoweave_b200.check_status()
+        assert torch.equal(sorted_idx(idx_g), sorted_idx(idx_e))
+        assert (out_g.float() - out_e.float()).abs().max().item() <= 2e-2  # the order inside a row is not promised
