@@ -409,6 +409,20 @@ def run_micro(args):
         ms = timed(lambda: sparse_attention_forward(q, kk, vv, pos, None, with_sum, with_sum, "bthd"), reps=3)
         out.append({"op": name, "shape": [T, S, TOPK], "ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak,
                     "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
+    # projection front-end on the benchmark's shape: 33 312 tokens, 16 heads + 4 indexer heads (VGGT grid positions)
+    from geoweave_b200.front_end import FrontEndParams, project_epilogue, rope_tables
+    del q, kk, vv, pos
+    N = 33312
+    width = 3 * H * D + 2 * HI * DI + HI
+    fused = torch.randn(1, N, width, device=dev).bfloat16()
+    fpos = torch.randint(0, 38, (1, N, 2), device=dev)
+    cos, sin = rope_tables(38, dev, torch.bfloat16)
+    vec = lambda: (torch.rand(64, device=dev) + 0.5, torch.randn(64, device=dev) * 0.1, 1e-5)
+    prm = FrontEndParams(torch.empty(0), None, H, HI, vec(), vec(), vec(), cos, sin)
+    ms = timed(lambda: project_epilogue(fused, fpos, prm))
+    nbytes = 2 * N * width * 2 + N * 16  # every value read once and written once, plus the positions
+    out.append({"op": "projection front-end epilogue (LayerNorm, rotary, layout), bf16", "shape": [N, width], "ms": ms, "bound": "hbm",
+                "achieved": nbytes / ms / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
     geoweave_b200.check_status()
     print(json.dumps({"micro": out}), flush=True)
 

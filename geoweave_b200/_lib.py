@@ -51,6 +51,9 @@ SIGNATURES = {
     "gw_sparse_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, _I64x3, _I64x3, _I64x3, c_float, c_void_p, _I64x3, c_void_p, c_void_p,
                                    c_void_p, c_void_p]),
+    "gw_project_epilogue": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                    c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
 }
 
 

@@ -137,6 +137,32 @@ int gw_sparse_attn_fwd(const void* q, const void* k, const void* v, const int32_
                        const int64_t v_strides[3], float scale, void* out, const int64_t out_strides[3], float* lse,
                        float* attn_sum, int* status_dev, gw_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Projection front-end (the step in front of stages 1-3): from the output of the layer's fused linear
+ * projection to the six operator inputs, in one pass.
+ *
+ * fused [tokens, ld] of `dtype` holds per token [q | k | v | idx_q | idx_k | idx_w]
+ * = 3*H*D + 2*Hi*Di + Hi values (qkv itself ordered [3][H][D]).  q, k: LayerNorm over D, then the 2-D rotary
+ * embedding; v: copied; idx_q: rotary; idx_k: LayerNorm, rotary; idx_w: copied.  pos int64 [tokens, 2] = (y, x)
+ * (null: no rotary embedding); cos_tab / sin_tab fp32 [table_rows, D/2], the tables of the reference's rotary
+ * module (columns j and j + D/4 hold the same angle); a position outside the tables sets the status word.
+ * Each LayerNorm is (weight, bias, eps) over 64 values, fp32, or null pointers for none.
+ * Outputs, all of `dtype`, contiguous and token-major: q, k, v [tokens, H, D]; q_idx, k_idx [tokens, Hi, Di];
+ * w [tokens, Hi] -- what gw_indexer_topk_fused and gw_sparse_attn_fwd read.
+ * Requirements: D = Di = 64; rows of `fused` start on 8-byte boundaries (ld a multiple of 4 for 16-bit types, of 2
+ *               for fp32); every pointer 16-byte aligned; Hi <= 32.
+ * Replaces: easyvolcap/official_vggt/layers/dsa_attention.py:587-627 (_project_qkv_and_indexer_fused after its
+ *           F.linear), :229-232 (_project_attention_qkv_from_flat), :4935-4941 (q_norm, k_norm, rope) and
+ *           :5309-5315 (the .contiguous() transposes); easyvolcap/official_vggt/layers/indexer.py:302-328
+ *           (LightningIndexer.project after its three linear layers); easyvolcap/official_vggt/layers/rope.py:134-188.
+ * ---------------------------------------------------------------------------------------------- */
+int gw_project_epilogue(const void* fused, int dtype, int64_t tokens, int64_t ld, int H, int D, int Hi, int Di,
+                        const int64_t* pos, const float* cos_tab, const float* sin_tab, int table_rows,
+                        const float* q_norm_w, const float* q_norm_b, float q_norm_eps, const float* k_norm_w,
+                        const float* k_norm_b, float k_norm_eps, const float* idx_k_norm_w, const float* idx_k_norm_b,
+                        float idx_k_norm_eps, void* q, void* k, void* v, void* q_idx, void* k_idx, void* w,
+                        int* status_dev, gw_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

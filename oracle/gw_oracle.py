@@ -237,3 +237,68 @@ def reference_cpu_path(q_idx, k_idx, w, q, k, v, topk: int, idx_scale: float, at
     attn = sc.softmax(dim=-1)
     out = torch.matmul(attn.unsqueeze(-2), gather(v)).squeeze(-2)
     return out, idx
+
+
+# ---------------------------------------------------------------------------------------------
+# projection front-end: what DSAAttention.forward does between its fused linear layer and the operator calls
+# ---------------------------------------------------------------------------------------------
+def _layer_norm(x, weight, bias, eps):
+    """LayerNorm over the last dimension (biased variance), as torch.nn.LayerNorm."""
+    mean = x.mean(-1, keepdim=True)
+    var = ((x - mean) ** 2).mean(-1, keepdim=True)
+    y = (x - mean) / torch.sqrt(var + eps)
+    if weight is not None:
+        y = y * weight + bias
+    return y
+
+
+def _rope_2d(tokens, pos, cos_tab, sin_tab):
+    """2-D rotary embedding of ``tokens [B,N,heads,D]`` at integer positions ``pos [B,N,2]`` (y, x).
+
+    The first half of the head dimension is rotated by the y position, the second by the x position; inside a
+    half of width F the pairs are (j, j + F/2) and both members use table column j mod F/2 (the tables hold
+    cat(angles, angles)) -- official_vggt/layers/rope.py:117-188.
+    """
+    D = tokens.shape[-1]
+    F_ = D // 2
+    out = torch.empty_like(tokens)
+    for half, axis in ((slice(0, F_), 0), (slice(F_, D), 1)):
+        t = tokens[..., half]
+        cos = cos_tab[pos[..., axis]][:, :, None, :]  # [B,N,1,F]
+        sin = sin_tab[pos[..., axis]][:, :, None, :]
+        rot = torch.cat((-t[..., F_ // 2:], t[..., : F_ // 2]), dim=-1)
+        out[..., half] = t * cos + rot * sin
+    return out
+
+
+def project_front_end(fused, pos, cos_tab, sin_tab, heads, head_dim, idx_heads, idx_dim, q_norm=None, k_norm=None,
+                      idx_k_norm=None):
+    """From the output of the fused linear layer to the six operator inputs, fp32 math.
+
+    ``fused [B,N,3*H*D + 2*Hi*Di + Hi]`` holds, per token, [q | k | v | idx_q | idx_k | idx_w] in that order
+    (dsa_attention.py:545-600: the weights of qkv, q_proj, k_proj, w_proj are concatenated; qkv itself is
+    [3][H][D], :229-232).  q and k get LayerNorm over the head dimension, then the 2-D rotary embedding (:4935-4941);
+    idx_k gets its LayerNorm, idx_q and idx_k the same rotary embedding, idx_w is passed through (indexer.py:302-328).
+    Each ``*_norm`` is ``(weight, bias, eps)`` or None.  Returns ``q, k, v [B,N,H,D]``, ``q_idx, k_idx [B,N,Hi,Di]``,
+    ``w [B,N,Hi]``, all fp32.
+    """
+    f = _f32(fused)
+    B, N, _ = f.shape
+    H, D, Hi, Di = heads, head_dim, idx_heads, idx_dim
+    pos = torch.as_tensor(pos).to(torch.int64)
+    cos_tab, sin_tab = _f32(cos_tab), _f32(sin_tab)
+    qkv = f[..., : 3 * H * D].reshape(B, N, 3, H, D)
+    o = 3 * H * D
+    iq = f[..., o: o + Hi * Di].reshape(B, N, Hi, Di)
+    ik = f[..., o + Hi * Di: o + 2 * Hi * Di].reshape(B, N, Hi, Di)
+    w = f[..., o + 2 * Hi * Di: o + 2 * Hi * Di + Hi].clone()
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2].clone()
+
+    def norm(x, prm):
+        return x if prm is None else _layer_norm(x, _f32(prm[0]), _f32(prm[1]), float(prm[2]))
+
+    q = _rope_2d(norm(q, q_norm), pos, cos_tab, sin_tab)
+    k = _rope_2d(norm(k, k_norm), pos, cos_tab, sin_tab)
+    iq = _rope_2d(iq, pos, cos_tab, sin_tab)
+    ik = _rope_2d(norm(ik, idx_k_norm), pos, cos_tab, sin_tab)
+    return q, k, v, iq, ik, w

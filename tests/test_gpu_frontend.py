@@ -1,0 +1,134 @@
+"""GPU parity of the projection front-end (the step in front of the indexer and the sparse attention) through the C ABI,
+against fixtures made by the reference's own modules and against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gw_oracle as orc
+from tests import golden
+from tests.gpu_util import dev
+
+pytestmark = pytest.mark.gpu
+
+NAMES = ["q", "k", "v", "q_idx", "k_idx", "w"]
+
+
+@pytest.fixture(scope="module")
+def fe_golden():
+    return golden.load("reference_frontend.npz")
+
+
+def T(a, dtype=None):
+    t = torch.from_numpy(np.asarray(a))
+    return t if dtype is None else t.to(dtype)
+
+
+def params_of(c, device, table_dtype):
+    from geoweave_b200.front_end import FrontEndParams
+
+    ln = lambda w, b, eps: (T(c[w]).to(device), T(c[b]).to(device), float(c[eps]))
+    return FrontEndParams(T(c["weight"]).to(device), T(c["bias"]).to(device), int(c["heads"]), 4,
+                          ln("q_norm_w", "q_norm_b", "eps"), ln("k_norm_w", "k_norm_b", "eps"),
+                          ln("ik_norm_w", "ik_norm_b", "ik_norm_eps"), T(c["cos"]).to(device), T(c["sin"]).to(device))
+
+
+def tolerance(ref, dtype):
+    # fp32: rounding order only.  16-bit: the reference rounds after every operation, this kernel once; two units in
+    # the last place of the result's magnitude cover that
+    if dtype == torch.float32:
+        return 2e-5 + 2e-6 * ref.abs()
+    return 2e-2 + 2.0 ** -7 * ref.abs()
+
+
+@pytest.mark.parametrize("name,dtype", [("fe_f32", torch.float32), ("fe_bf16", torch.bfloat16), ("fe_pi3_bf16", torch.bfloat16)])
+def test_epilogue_on_the_reference_linear_output(fe_golden, name, dtype):
+    import geoweave_b200
+    from geoweave_b200.front_end import project_epilogue
+
+    c = fe_golden[name]
+    prm = params_of(c, dev(), dtype)
+    outs = project_epilogue(T(c["fused"], dtype).to(dev()), T(c["pos"]).to(dev()), prm)
+    geoweave_b200.check_status()
+    for nm, o in zip(NAMES, outs):
+        ref = T(c[nm])
+        assert o.dtype == dtype and tuple(o.shape) == tuple(ref.shape) and o.is_contiguous(), nm
+        err = (o.float().cpu() - ref).abs()
+        assert bool((err <= tolerance(ref, dtype)).all()), (name, nm, float(err.max()))
+    assert torch.equal(outs[2].float().cpu(), T(c["v"])) and torch.equal(outs[5].float().cpu(), T(c["w"]))  # copies are exact
+
+
+@pytest.mark.parametrize("name,dtype", [("fe_f32", torch.float32), ("fe_bf16", torch.bfloat16)])
+def test_linear_plus_epilogue_from_the_layer_input(fe_golden, name, dtype):
+    from geoweave_b200.front_end import project_qkv_and_indexer
+
+    c = fe_golden[name]
+    prm = params_of(c, dev(), dtype)
+    prm.weight, prm.bias = prm.weight.to(dtype), prm.bias.to(dtype)
+    outs = project_qkv_and_indexer(T(c["x"], dtype).to(dev()), T(c["pos"]).to(dev()), prm)
+    for nm, o in zip(NAMES, outs):
+        ref = T(c[nm])
+        err = (o.float().cpu() - ref).abs()
+        # the GEMM runs on another device with another summation order: one more unit in the last place
+        assert bool((err <= 2 * tolerance(ref, dtype) + (1e-4 if dtype == torch.float32 else 0)).all()), (name, nm, float(err.max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("heads,views", [(16, 8), (8, 3)])
+def test_production_width_against_the_oracle(dtype, heads, views):
+    """16 heads, VGGT token grid (5 special tokens at position 0 + 28 x 37 patches per view), some parts switched off."""
+    from geoweave_b200.front_end import FrontEndParams, project_epilogue, rope_tables
+
+    g = torch.Generator().manual_seed(heads * 100 + views)
+    n_tok = 5 + 28 * 37
+    N = views * n_tok
+    width = 3 * heads * 64 + 2 * 4 * 64 + 4
+    fused = (torch.randn(1, N, width, generator=g) * 1.5 + 0.3).to(dtype)
+    ys, xs = torch.meshgrid(torch.arange(28), torch.arange(37), indexing="ij")
+    grid = torch.stack([ys.reshape(-1), xs.reshape(-1)], -1) + 1
+    pos = torch.cat([torch.zeros(5, 2, dtype=torch.int64), grid]).repeat(views, 1).view(1, N, 2)
+    cos, sin = rope_tables(38, "cpu", dtype)
+    vec = lambda: (torch.randn(64, generator=g) * 0.3 + 1.0, torch.randn(64, generator=g) * 0.2, 1e-5)
+    prm = FrontEndParams(torch.empty(0), None, heads, 4, vec(), None if heads == 8 else vec(), vec(), cos, sin)
+    outs = project_epilogue(fused.to(dev()), pos.to(dev()), prm)
+    refs = orc.project_front_end(fused, pos, cos, sin, heads, 64, 4, 64, prm.q_norm, prm.k_norm, prm.idx_k_norm)
+    for nm, o, ref in zip(NAMES, outs, refs):
+        err = (o.float().cpu() - ref).abs()
+        tol = 2e-5 + 2e-6 * ref.abs() if dtype == torch.float32 else 2.0 ** -7 * ref.abs() + 1e-3  # one unit in the last place
+        assert bool((err <= tol).all()), (nm, float(err.max()))
+    # without positions: no rotary embedding
+    outs_np = project_epilogue(fused.to(dev()), None, prm)
+    refs_np = orc.project_front_end(fused, torch.zeros_like(pos), torch.ones(1, 32), torch.zeros(1, 32), heads, 64, 4, 64,
+                                    prm.q_norm, prm.k_norm, prm.idx_k_norm)
+    assert (outs_np[0].float().cpu() - refs_np[0]).abs().max().item() <= (1e-4 if dtype == torch.float32 else 6e-2)
+
+
+def test_front_end_feeds_the_operators_and_refuses_bad_input():
+    """The six outputs go straight into the indexer and the attention; wrong widths and positions outside the
+    tables are reported."""
+    import geoweave_b200
+    from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_inference_func
+    from geoweave_b200.front_end import FrontEndParams, project_epilogue, rope_tables
+
+    g = torch.Generator().manual_seed(9)
+    N, heads = 4164, 16
+    width = 3 * heads * 64 + 2 * 4 * 64 + 4
+    fused = torch.randn(1, N, width, generator=g).bfloat16()
+    pos = torch.randint(0, 30, (1, N, 2), generator=g)
+    cos, sin = rope_tables(30, "cpu", torch.bfloat16)
+    prm = FrontEndParams(torch.empty(0), None, heads, 4, None, None, None, cos, sin)
+    q, k, v, qi, ki, w = project_epilogue(fused.to(dev()), pos.to(dev()), prm)
+    idx, _ = sparse_topk_indexer_inference_func(qi, ki, w, None, 256, 0.125, return_scores=False)
+    out, _ = sparse_index_flash_attn_inference_func(q, k, v, idx, None, False, 0.125)
+    geoweave_b200.check_status()
+    refs = orc.project_front_end(fused, pos, cos, sin, heads, 64, 4, 64)
+    rows = torch.arange(0, N, 97)
+    scores = orc.indexer_scores(refs[3].bfloat16()[:, rows], refs[4].bfloat16(), refs[5].bfloat16(), 0.125)
+    res = orc.audit_topk(idx[:, rows.to(dev())], scores, 256, refs[3].bfloat16()[:, rows], refs[4].bfloat16(), refs[5].bfloat16(), 0.125)
+    assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
+    assert out.shape == (1, N, heads, 64) and bool(torch.isfinite(out.float()).all())
+    with pytest.raises(ValueError):
+        project_epilogue(fused[..., :-2].to(dev()), pos.to(dev()), prm)
+    project_epilogue(fused.to(dev()), (pos + 25).to(dev()), prm)   # positions up to 54 against tables of 30 rows
+    with pytest.raises(geoweave_b200.GeoWeaveError):
+        geoweave_b200.check_status()

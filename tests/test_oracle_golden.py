@@ -107,3 +107,42 @@ def test_merge_two_topk_equals_topk_of_union():
     m_s, m_i = orc.merge_two_topk(sc.gather(-1, a_i.long()), a_i, sc.gather(-1, b_i.long()), b_i, k)
     assert torch.equal(m_i, orc.topk_tie_exact(sc, k))
     assert torch.equal(m_s, sc.gather(-1, m_i.long()))
+
+
+@pytest.mark.parametrize("name", ["fe_f32", "fe_bf16", "fe_pi3_bf16"])
+def test_front_end_restatement_matches_the_reference_modules(name):
+    """q/k LayerNorm + rotary embedding, v, and the indexer's projections after the fused linear layer
+    (fixtures from DSAAttention / LightningIndexer / RotaryPositionEmbedding2D run on CPU)."""
+    import numpy as np
+
+    from tests import golden as golden_pkg
+
+    c = golden_pkg.load("reference_frontend.npz")[name]
+    T = lambda a: torch.from_numpy(np.asarray(a))
+    outs = orc.project_front_end(T(c["fused"]), T(c["pos"]), T(c["cos"]), T(c["sin"]), int(c["heads"]), 64, 4, 64,
+                                 (T(c["q_norm_w"]), T(c["q_norm_b"]), float(c["eps"])),
+                                 (T(c["k_norm_w"]), T(c["k_norm_b"]), float(c["eps"])),
+                                 (T(c["ik_norm_w"]), T(c["ik_norm_b"]), float(c["ik_norm_eps"])))
+    exact = name == "fe_f32"
+    for nm, o in zip(["q", "k", "v", "q_idx", "k_idx", "w"], outs):
+        ref = T(c[nm])
+        err = (o - ref).abs()
+        # fp32 modules: rounding order only; bf16 modules round after every operation (two units in the last place)
+        tol = 2e-5 + 2e-6 * ref.abs() if exact else 2e-2 + 2.0 ** -7 * ref.abs()
+        assert bool((err <= tol).all()), (nm, float(err.max()))
+    # the linear layer itself: x @ weight^T + bias reproduces the recorded output
+    lin = torch.nn.functional.linear(T(c["x"]), T(c["weight"]), T(c["bias"]))
+    assert (lin - T(c["fused"])).abs().max().item() <= (1e-4 if exact else 6e-2)
+
+
+def test_rope_tables_follow_the_reference_rounding():
+    import numpy as np
+
+    from geoweave_b200.front_end import rope_tables
+    from tests import golden as golden_pkg
+
+    G = golden_pkg.load("reference_frontend.npz")
+    for name, dtype in (("fe_f32", torch.float32), ("fe_bf16", torch.bfloat16)):
+        c = G[name]
+        cos, sin = rope_tables(c["cos"].shape[0], "cpu", dtype)
+        assert torch.equal(cos, torch.from_numpy(np.asarray(c["cos"]))) and torch.equal(sin, torch.from_numpy(np.asarray(c["sin"])))
