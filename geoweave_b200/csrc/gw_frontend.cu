@@ -108,7 +108,7 @@ __device__ __forceinline__ void head_rope(float (&t)[8], const float (&cs)[8], c
 }
 
 template <typename T>
-__global__ void __launch_bounds__(FE_WARPS * 32) project_epilogue_kernel(const FeParams p) {
+__global__ void __launch_bounds__(FE_WARPS * 32, 3) project_epilogue_kernel(const FeParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * FE_WARPS + (threadIdx.x >> 5);
   const int64_t nwarps = static_cast<int64_t>(gridDim.x) * FE_WARPS;
@@ -119,15 +119,6 @@ __global__ void __launch_bounds__(FE_WARPS * 32) project_epilogue_kernel(const F
   const int col = 8 * (sub & 3);             // first column inside the half = column of the tables
   const bool first16 = (sub & 3) < 2;
   const bool ln_q = p.qn_w != nullptr, ln_k = p.kn_w != nullptr, ln_i = p.in_w != nullptr, rope = p.pos != nullptr;
-  float qw[8], qb[8], kw[8], kb[8];
-  if (ln_q) {
-    load8(p.qn_w + e, qw);
-    load8(p.qn_b + e, qb);
-  }
-  if (ln_k) {
-    load8(p.kn_w + e, kw);
-    load8(p.kn_b + e, kb);
-  }
   const T* fused = static_cast<const T*>(p.fused);
 
   for (int64_t tok = warp0; tok < p.tokens; tok += nwarps) {
@@ -155,8 +146,20 @@ __global__ void __launch_bounds__(FE_WARPS * 32) project_epilogue_kernel(const F
         load8(row + (H + h) * 64 + e, b, al16);
         load8(row + (2 * H + h) * 64 + e, c, al16);
       }
-      if (ln_q) head_layer_norm(a, qw, qb, p.qn_eps);
-      if (ln_k) head_layer_norm(b, kw, kb, p.kn_eps);
+      // the LayerNorm vectors are re-read every turn (they stay in L1): holding them in registers would cost a
+      // third of the resident warps, and this kernel lives on loads in flight
+      if (ln_q) {
+        float w8[8], b8[8];
+        load8(p.qn_w + e, w8);
+        load8(p.qn_b + e, b8);
+        head_layer_norm(a, w8, b8, p.qn_eps);
+      }
+      if (ln_k) {
+        float w8[8], b8[8];
+        load8(p.kn_w + e, w8);
+        load8(p.kn_b + e, b8);
+        head_layer_norm(b, w8, b8, p.kn_eps);
+      }
       if (rope) {
         head_rope(a, cs, sn, first16);
         head_rope(b, cs, sn, first16);
