@@ -423,6 +423,17 @@ def run_micro(args):
     nbytes = 2 * N * width * 2 + N * 16  # every value read once and written once, plus the positions
     out.append({"op": "projection front-end epilogue (LayerNorm, rotary, layout), bf16", "shape": [N, width], "ms": ms, "bound": "hbm",
                 "achieved": nbytes / ms / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
+    # the whole layer as one call: fused projection (library GEMM) -> front-end -> indexer -> attention
+    from geoweave_b200.layer import SparseGlobalAttentionLayer
+    dim = H * D
+    prm = FrontEndParams((torch.randn(width, dim, device=dev) * dim ** -0.5).bfloat16(), torch.zeros(width, device=dev).bfloat16(),
+                         H, HI, vec(), vec(), vec(), cos, sin)
+    x = torch.randn(1, N, dim, device=dev).bfloat16()
+    for graph in (False, True):
+        layer = SparseGlobalAttentionLayer(prm, TOPK, use_cuda_graph=graph)
+        ms = timed(lambda: layer(x, fpos), reps=3)
+        out.append({"op": "whole layer: projection + front-end + indexer + attention" + (", CUDA graph" if graph else ", eager"),
+                    "shape": [N, dim, TOPK], "ms": ms, "tokens_per_s": N / ms * 1e3})
     geoweave_b200.check_status()
     print(json.dumps({"micro": out}), flush=True)
 

@@ -132,3 +132,39 @@ def test_front_end_feeds_the_operators_and_refuses_bad_input():
     project_epilogue(fused.to(dev()), (pos + 25).to(dev()), prm)   # positions up to 54 against tables of 30 rows
     with pytest.raises(geoweave_b200.GeoWeaveError):
         geoweave_b200.check_status()
+
+
+def test_whole_layer_eager_graph_and_reused_indices():
+    """fused projection -> front-end -> indexer -> attention as one call; the CUDA-graph replay gives what the eager
+    chain gives, and a layer that reuses another layer's indices skips its indexer."""
+    import geoweave_b200
+    from geoweave_b200.front_end import FrontEndParams, rope_tables
+    from geoweave_b200.layer import SparseGlobalAttentionLayer
+
+    g = torch.Generator().manual_seed(21)
+    N, heads, dim, k = 8328, 16, 256, 256
+    width = 3 * heads * 64 + 2 * 4 * 64 + 4
+    weight = (torch.randn(width, dim, generator=g) * dim ** -0.5).bfloat16().to(dev())
+    bias = (torch.randn(width, generator=g) * 0.1).bfloat16().to(dev())
+    cos, sin = rope_tables(40, dev(), torch.bfloat16)
+    vec = lambda: ((torch.rand(64, generator=g) + 0.5).to(dev()), (torch.randn(64, generator=g) * 0.1).to(dev()), 1e-5)
+    prm = FrontEndParams(weight, bias, heads, 4, vec(), vec(), vec(), cos, sin)
+    eager = SparseGlobalAttentionLayer(prm, k)
+    graphed = SparseGlobalAttentionLayer(prm, k, use_cuda_graph=True)
+    for trial in range(2):
+        x = torch.randn(1, N, dim, generator=g).bfloat16().to(dev())
+        pos = torch.randint(0, 40, (1, N, 2), generator=g).to(dev())
+        out_e, idx_e = eager(x, pos)
+        out_g, idx_g = graphed(x, pos)
+        geoweave_b200.check_status()
+        assert out_e.shape == (1, N, heads * 64) and idx_e.shape == (1, N, k)
+        assert torch.equal(torch.sort(idx_e.long(), -1).values, torch.sort(idx_g.long(), -1).values)
+        assert (out_e.float() - out_g.float()).abs().max().item() <= 2e-2
+        # a second layer on the same tokens that takes these indices: same attention as handing them over by hand
+        out_r, idx_r = eager(x, pos, reuse_topk_indices=idx_e)
+        assert idx_r.data_ptr() == idx_e.data_ptr() or torch.equal(idx_r, idx_e)
+        assert (out_r.float() - out_e.float()).abs().max().item() <= 2e-2
+        out_rg, _ = graphed(x, pos, reuse_topk_indices=idx_e)
+        assert (out_rg.float() - out_e.float()).abs().max().item() <= 2e-2
+    with pytest.raises(ValueError):
+        eager(x, pos, reuse_topk_indices=idx_e[:, :10])
