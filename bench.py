@@ -157,6 +157,29 @@ class Clocks:
 # ---------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
+def bind_host_thread_near_gpu(dev) -> str:
+    """Run this process (and place its pinned buffers) on the CPUs next to its GPU.  With one rank per GPU the
+    host->device copies of all ranks run at once; a rank whose pinned pages sit on the other socket copies at a
+    fraction of the link rate.  Only reads the topology (NVML) and sets this process's own CPU affinity."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(dev).uuid)
+        handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        n_cpu = os.cpu_count() or 1
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, (n_cpu + 63) // 64)
+        near = {i for i in range(n_cpu) if (int(mask[i // 64]) >> (i % 64)) & 1}
+        allowed = os.sched_getaffinity(0)
+        pick = near & allowed
+        if pick and pick != allowed:
+            os.sched_setaffinity(0, pick)
+            return f"{len(pick)} of {len(allowed)} CPUs"
+        return "unchanged"
+    except Exception as exc:  # no NVML, no permission: measure where we are
+        return f"unavailable ({type(exc).__name__})"
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -164,7 +187,7 @@ def run_ours(args):
     from geoweave_b200 import _lib
     from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
     from geoweave_b200.custom_indexer import sparse_topk_indexer_inference_func
-    from geoweave_b200.sharding import gather_rows, gather_rows_async, row_partition
+    from geoweave_b200.sharding import gather_rows_packed, row_partition
 
     _lib.load()  # fail loudly if the CUDA library is missing: there is no other path
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -172,6 +195,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    host_binding = bind_host_thread_near_gpu(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     views, tpv, layers, desc = WORKLOADS[args.workload]
@@ -204,8 +228,8 @@ def run_ours(args):
 
     def layer_op(t, record):
         if world > 1:  # the indexer needs K_idx and w; K and V are gathered behind it
-            k_idx, w = gather_rows(t["k_idx"], n_tokens), gather_rows(t["w"], n_tokens)
-            k_pend, v_pend = gather_rows_async(t["k"], n_tokens), gather_rows_async(t["v"], n_tokens)
+            k_idx, w = [x.contiguous() for x in gather_rows_packed([t["k_idx"], t["w"]], n_tokens).result()]
+            kv_pend = gather_rows_packed([t["k"], t["v"]], n_tokens, async_op=True)
         else:
             k_idx, w, k, v = t["k_idx"], t["w"], t["k"], t["v"]
         if record:
@@ -215,7 +239,7 @@ def run_ours(args):
         if record:
             e1.record()
         if world > 1:
-            k, v = k_pend.result(), v_pend.result()
+            k, v = kv_pend.result()
         out, _ = sparse_index_flash_attn_inference_func(t["q"], k, v, idx, None, False, D ** -0.5, False)
         if record:
             e2.record()
@@ -228,20 +252,28 @@ def run_ours(args):
 
     def step_e2e():
         """Every layer: pinned host inputs -> device (copy stream), the three stages (main stream), output ->
-        pinned host (second copy stream); copies of neighbouring layers overlap the kernels."""
+        pinned host (second copy stream).  The copy of layer i+1 is ENQUEUED before the kernels of layer i, so it
+        overlaps them whether or not the host thread runs ahead of the device."""
         main = torch.cuda.current_stream(dev)
-        used = [None, None]  # event: kernels that read staging set i have finished
-        for layer in range(layers):
+        used = [None, None]    # event: kernels that read staging set i have finished
+        ready = [None, None]   # event: staging set i holds its layer's inputs
+
+        def enqueue_copy_in(layer):
             st = staging[layer & 1]
             with torch.cuda.stream(copy_in):
                 if used[layer & 1] is not None:
                     copy_in.wait_event(used[layer & 1])
                 for n, x in host[layer].items():
                     st[n].copy_(x, non_blocking=True)
-                ready = torch.cuda.Event()
-                ready.record(copy_in)
-            main.wait_event(ready)
-            out = layer_op(st, False)
+                ready[layer & 1] = torch.cuda.Event()
+                ready[layer & 1].record(copy_in)
+
+        enqueue_copy_in(0)
+        for layer in range(layers):
+            main.wait_event(ready[layer & 1])
+            if layer + 1 < layers:
+                enqueue_copy_in(layer + 1)  # the other staging set: free once layer - 1 has finished
+            out = layer_op(staging[layer & 1], False)
             done = torch.cuda.Event()
             done.record(main)
             used[layer & 1] = done
@@ -277,11 +309,22 @@ def run_ours(args):
     t_begin = time.perf_counter()
     ms_total = timed(lambda: step_resident(True), args.steps)
     t_end = time.perf_counter()
+    h2d_gbs = None
     if args.profile:
         ms_e2e = float("nan")
     else:
         step_e2e()
         ms_e2e = timed(step_e2e, args.steps)
+
+        def copies_only():  # the same host->device copies with nothing else running: the link rate this rank gets
+            with torch.cuda.stream(copy_in):
+                for layer in range(layers):
+                    for n, x in host[layer].items():
+                        staging[layer & 1][n].copy_(x, non_blocking=True)
+            torch.cuda.synchronize()
+
+        ms_copy = timed(copies_only, 2) / 2
+        h2d_gbs = h2d / ms_copy / 1e6
     geoweave_b200.check_status()
     clk = clocks.stop(t_begin, time.perf_counter()) if clocks else None
 
@@ -314,7 +357,7 @@ def run_ours(args):
                 "ms_per_step": ms_step, "ms_per_layer": ms_step / layers, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_of(args, n_tokens, layers, desc, world),
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": ms_e2e / args.steps},
+                        "ms_per_step": ms_e2e / args.steps, "h2d_alone_gbs_rank0_clock": h2d_gbs, "host_binding": host_binding},
                 "gpu_launches": launches * args.steps,
                 "roofline": {"kernel": "sparse_attn_mma_kernel (stage 3 gather)", "bound": "hbm", "achieved": attn_gbs, "peak": hbm_peak,
                              "unit": "GB/s", "frac": attn_gbs / hbm_peak, "traffic": attn_traffic, "peak_source": peak_src,

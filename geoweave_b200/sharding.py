@@ -1,6 +1,6 @@
 """Multi-GPU form of the path: query rows are split into contiguous slices, one per rank; every rank needs
-all keys, so K, V, K_idx and w are all-gathered once per layer (NCCL over NVLink) and nothing else is
-exchanged.  The reference has no multi-GPU form of this op; the split follows its own single-GPU
+all keys, so K_idx with w, and K with V, are all-gathered once per layer (two collectives, NCCL over NVLink) and
+nothing else is exchanged.  The reference has no multi-GPU form of this op; the split follows its own single-GPU
 query-chunk loop, which keeps K/V/K_idx resident and walks query chunks
 (easyvolcap/official_vggt/layers/dsa_attention.py:1138-1264, ``_run_sparse_streaming_direct``).
 """
@@ -11,7 +11,7 @@ from typing import List, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["row_partition", "shard_rows", "gather_rows", "gather_rows_async", "sparse_global_attention_sharded"]
+__all__ = ["row_partition", "shard_rows", "gather_rows", "gather_rows_async", "gather_rows_packed", "sparse_global_attention_sharded"]
 
 
 def row_partition(n_rows: int, world_size: int) -> List[Tuple[int, int]]:
@@ -92,6 +92,41 @@ def _gather_rows(x: torch.Tensor, n_rows: int, group, dim: int, async_op: bool) 
     return _PendingGather(work if async_op else None, finish)
 
 
+class _PendingPacked:
+    def __init__(self, pending: _PendingGather, split):
+        self._pending, self._split, self._out = pending, split, None
+
+    def result(self):
+        if self._out is None:
+            self._out = self._split(self._pending.result())
+        return self._out
+
+
+def gather_rows_packed(xs: Sequence[torch.Tensor], n_rows: int, group=None, async_op: bool = False) -> _PendingPacked:
+    """All-gather several row-sharded tensors ``[B, rows, ...]`` of one dtype with ONE collective: each token's values
+    are laid side by side, gathered, and handed back as views of the gathered buffer (token stride = the packed
+    width; the last dimension of every view stays contiguous, which is all the attention operator asks of K and V).
+    One collective instead of two saves a launch and a latency per layer, which shows at eight ranks where the
+    whole layer takes under 2 ms.  ``result()`` returns the list of full tensors."""
+    xs = list(xs)
+    if len({x.dtype for x in xs}) != 1 or len({tuple(x.shape[:2]) for x in xs}) != 1:
+        raise ValueError("packed tensors must share dtype, batch and row count")
+    B, rows = xs[0].shape[:2]
+    widths = [int(x[0, 0].numel()) if rows > 0 else int(torch.Size(x.shape[2:]).numel()) for x in xs]
+    tails = [tuple(x.shape[2:]) for x in xs]
+    packed = torch.cat([x.reshape(B, rows, wd) for x, wd in zip(xs, widths)], dim=-1)
+    pending = _gather_rows(packed, n_rows, group, 1, async_op)
+
+    def split(full):
+        out, off = [], 0
+        for wd, tail in zip(widths, tails):
+            out.append(full[:, :, off: off + wd].unflatten(-1, tail) if len(tail) != 1 else full[:, :, off: off + wd])
+            off += wd
+        return out
+
+    return _PendingPacked(pending, split)
+
+
 def sparse_global_attention_sharded(q_idx, k_idx, w, q, k, v, topk: int, n_tokens: int, group=None,
                                     idx_scale=None, attn_scale=None, ops=None):
     """One layer of the path on this rank's token shard (all tensors ``[B, rows_of_this_rank, ...]``).
@@ -111,10 +146,9 @@ def sparse_global_attention_sharded(q_idx, k_idx, w, q, k, v, topk: int, n_token
             return sparse_index_flash_attn_inference_func(qq, kk_, vv, pos, None, False, sc, False)[0]
     else:
         indexer, attention = ops
-    k_idx_full = gather_rows(k_idx, n_tokens, group)
-    w_full = gather_rows(w, n_tokens, group)
-    k_pending = gather_rows_async(k, n_tokens, group)  # K and V arrive while the indexer runs
-    v_pending = gather_rows_async(v, n_tokens, group)
-    idx = indexer(q_idx, k_idx_full, w_full, topk, idx_scale)
-    out = attention(q, k_pending.result(), v_pending.result(), idx, attn_scale)
+    k_idx_full, w_full = gather_rows_packed([k_idx, w], n_tokens, group).result()
+    kv_pending = gather_rows_packed([k, v], n_tokens, group, async_op=True)  # K and V arrive while the indexer runs
+    idx = indexer(q_idx, k_idx_full.contiguous(), w_full.contiguous(), topk, idx_scale)
+    k_full, v_full = kv_pending.result()
+    out = attention(q, k_full, v_full, idx, attn_scale)
     return out, idx

@@ -33,7 +33,7 @@ def bf16_round(x):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     args = ap.parse_args()
     sys.dont_write_bytecode = True
     sys.path[:0] = [os.path.join(HERE, "_stubs"), args.reference]

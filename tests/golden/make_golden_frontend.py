@@ -28,7 +28,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     args = ap.parse_args()
     sys.dont_write_bytecode = True
     sys.path[:0] = [os.path.join(HERE, "_stubs"), args.reference]
