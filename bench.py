@@ -250,10 +250,14 @@ def run_ours(args):
         for layer in range(layers):
             layer_op(resident[layer], record)
 
+    enqueue_s = []  # host time spent enqueueing one end-to-end step (a step cannot be faster than this)
+    timeline = {} if os.environ.get("GW_BENCH_TIMELINE") == "1" else None
+
     def step_e2e():
         """Every layer: pinned host inputs -> device (copy stream), the three stages (main stream), output ->
         pinned host (second copy stream).  The copy of layer i+1 is ENQUEUED before the kernels of layer i, so it
         overlaps them whether or not the host thread runs ahead of the device."""
+        t_host = time.perf_counter()
         main = torch.cuda.current_stream(dev)
         used = [None, None]    # event: kernels that read staging set i have finished
         ready = [None, None]   # event: staging set i holds its layer's inputs
@@ -263,25 +267,43 @@ def run_ours(args):
             with torch.cuda.stream(copy_in):
                 if used[layer & 1] is not None:
                     copy_in.wait_event(used[layer & 1])
+                if timeline is not None:
+                    timeline.setdefault(layer, {})["h2d0"] = ev()
+                    timeline[layer]["h2d0"].record(copy_in)
                 for n, x in host[layer].items():
                     st[n].copy_(x, non_blocking=True)
-                ready[layer & 1] = torch.cuda.Event()
+                ready[layer & 1] = ev() if timeline is not None else torch.cuda.Event()
                 ready[layer & 1].record(copy_in)
+                if timeline is not None:
+                    timeline[layer]["h2d1"] = ready[layer & 1]
 
         enqueue_copy_in(0)
         for layer in range(layers):
             main.wait_event(ready[layer & 1])
             if layer + 1 < layers:
                 enqueue_copy_in(layer + 1)  # the other staging set: free once layer - 1 has finished
+            if timeline is not None:
+                timeline[layer]["c0"] = ev()
+                timeline[layer]["c0"].record(main)
             out = layer_op(staging[layer & 1], False)
-            done = torch.cuda.Event()
+            done = ev() if timeline is not None else torch.cuda.Event()
             done.record(main)
+            if timeline is not None:
+                timeline[layer]["c1"] = done
             used[layer & 1] = done
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(done)
                 out_host[layer].copy_(out, non_blocking=True)
                 out.record_stream(copy_out)
+        enqueue_s.append(time.perf_counter() - t_host)
         torch.cuda.synchronize()
+        if timeline is not None and rank == 0:  # GW_BENCH_TIMELINE=1: device times of one step, ms from its first copy
+            t0 = timeline[0]["h2d0"]
+            for layer in range(layers):
+                e = timeline[layer]
+                print(f"[timeline] layer {layer}: copy-in {t0.elapsed_time(e['h2d0']):.2f}-{t0.elapsed_time(e['h2d1']):.2f}  "
+                      f"kernels {t0.elapsed_time(e['c0']):.2f}-{t0.elapsed_time(e['c1']):.2f}", file=sys.stderr, flush=True)
+            timeline.clear()
 
     def barrier():
         if world > 1:
@@ -357,7 +379,8 @@ def run_ours(args):
                 "ms_per_step": ms_step, "ms_per_layer": ms_step / layers, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_of(args, n_tokens, layers, desc, world),
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": ms_e2e / args.steps, "h2d_alone_gbs_rank0_clock": h2d_gbs, "host_binding": host_binding},
+                        "ms_per_step": ms_e2e / args.steps, "h2d_alone_gbs_rank0_clock": h2d_gbs, "host_binding": host_binding,
+                        "host_enqueue_ms_per_step": (1e3 * statistics.median(enqueue_s)) if enqueue_s else None},
                 "gpu_launches": launches * args.steps,
                 "roofline": {"kernel": "sparse_attn_mma_kernel (stage 3 gather)", "bound": "hbm", "achieved": attn_gbs, "peak": hbm_peak,
                              "unit": "GB/s", "frac": attn_gbs / hbm_peak, "traffic": attn_traffic, "peak_source": peak_src,
