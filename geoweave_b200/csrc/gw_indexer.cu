@@ -485,6 +485,9 @@ SamplePlan plan_sample(int S, int k) {
   // least 1024 sampled keys and at most one key in 16 (the sampled pass is extra tensor-core work)
   int step = k / 32;
   if (step < 16) step = 16;
+  // very long key sets: no more than about 4096 sampled keys (the sampled pass and the threshold kernel grow
+  // with their number), as long as k / step stays at 8 or more; the lists then hold somewhat more candidates
+  if (S / 4096 > step) step = S / 4096 < k / 8 ? S / 4096 : (k / 8 > step ? k / 8 : step);
   if (step > S / 1024) step = S / 1024;
   if (step < 2) return sp;
   step |= 1;  // odd: never in lock-step with an even token grid

@@ -129,7 +129,11 @@ __device__ int warp_select_tight(const Lists& L, int k, uint32_t lo, uint32_t hi
     // the boundary bin becomes the new range (the end bins of the first level are open-ended)
     const uint32_t new_lo = (level == 0 && b_star == 0) ? 0u : cur_lo + (b_star << shift);
     uint32_t new_hi = cur_lo + (b_star << shift) + ((1u << shift) - 1u);
-    if (new_hi > cur_hi || new_hi < cur_lo) new_hi = cur_hi;
+    if (new_hi < cur_lo) new_hi = 0xffffffffu;  // the bin's upper edge lies beyond the key space
+    // Below the first level the range is closed (keys outside it were not counted), so its last bin may be cut
+    // short.  On the first level hi is a hint: keys above it were still counted in the bin their value falls in,
+    // and cutting that bin at hi would make the output pass take them on top of the k it was promised.
+    if (level > 0 && new_hi > cur_hi) new_hi = cur_hi;
     if (level == 0 && b_star == TS_BINS - 1) new_hi = 0xffffffffu;
     cur_lo = new_lo;
     cur_hi = new_hi;
