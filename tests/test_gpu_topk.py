@@ -73,6 +73,37 @@ def test_topk_exact_16bit_scores(dtype):
     assert torch.equal(vals.cpu(), sc.gather(-1, pos.cpu()))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cols,k", [(16384, 512), (33312, 1024)])
+def test_topk_exact_16bit_scores_on_the_sampled_path(dtype, cols, k):
+    """Wide 16-bit rows: plain loads into shared memory, sampled threshold, and boundaries crowded with equal values."""
+    from geoweave_b200.custom_indexer.topk_exact_cuda import topk_exact_select
+
+    g = torch.Generator().manual_seed(cols + k)
+    sc = (torch.randn(1, 40, cols, generator=g) * 2.0).to(dtype)
+    vals, pos = topk_exact_select(sc.to(dev()), k=k)
+    assert torch.equal(sorted_idx(pos), orc.topk_tie_exact(sc.float(), k).long())
+    assert torch.equal(vals.cpu(), sc.gather(-1, pos.cpu()))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_merge_two_topk_16bit_scores(dtype):
+    from geoweave_b200.custom_indexer.merge_two_topk_cuda import merge_two_topk_inplace
+
+    g = torch.Generator().manual_seed(17)
+    rows, k, start = 33, 1024, 20000
+    a_s = torch.randn(1, rows, k, generator=g).to(dtype)
+    b_s = torch.randn(1, rows, k, generator=g).to(dtype)
+    a_i = torch.stack([torch.randperm(start, generator=g)[:k] for _ in range(rows)]).view(1, rows, k).to(torch.int32)
+    b_p = torch.stack([torch.randperm(9000, generator=g)[:k] for _ in range(rows)]).view(1, rows, k)
+    exp_s, exp_i = orc.merge_two_topk(a_s.float(), a_i, b_s.float(), b_p + start, k)
+    o_s, o_i = torch.empty_like(a_s, device=dev()), torch.empty_like(a_i, device=dev())
+    assert merge_two_topk_inplace(a_s.to(dev()), a_i.to(dev()), b_s.to(dev()), b_p.to(dev()), start, o_s, o_i) is True
+    order = torch.sort(o_i.long(), -1)
+    assert torch.equal(order.values.cpu(), exp_i.long())
+    assert torch.equal(o_s.gather(-1, order.indices).float().cpu(), exp_s)
+
+
 def test_topk_exact_rejects_short_rows():
     from geoweave_b200.custom_indexer.topk_exact_cuda import topk_exact_select
 
