@@ -564,6 +564,10 @@ WsLayout ws_layout(int T, int S, int k) {
   // processed in chunks of whole waves of row blocks (about 2 GiB of lists per chunk)
   const size_t robust_row_bytes = static_cast<size_t>(2) * L.caph * 8;
   int chunk_blocks = static_cast<int>((static_cast<size_t>(2) << 30) / (robust_row_bytes * 5 / 4) / BM);
+  if (sp.m > 0) {  // the sampled scores of a chunk (fp32 [rows, m]) stay below about 1 GiB as well
+    const int by_sample = static_cast<int>((static_cast<size_t>(1) << 30) / (static_cast<size_t>(L.m_pad) * 4) / BM);
+    if (by_sample < chunk_blocks) chunk_blocks = by_sample;
+  }
   chunk_blocks = chunk_blocks >= 2 * MAX_SLOTS ? chunk_blocks / kPlanSms * kPlanSms : (chunk_blocks > 0 ? chunk_blocks : 1);
   if (chunk_blocks > nblocks) chunk_blocks = nblocks;
   L.chunk_rows = sp.step > 0 ? chunk_blocks * BM : 0;

@@ -268,6 +268,7 @@ def test_batch_of_two_on_the_fast_path():
     (33312, 2048, True, 384),     # 10 % duplicated key rows
     (133248, 1024, False, 384),   # 128 views
     (532992, 1024, False, 160),   # 512 views: several row chunks, 8328 key tiles
+    (532992, 256, False, 96),     # small k against a long key set: many sampled keys, chunks bounded by the sample buffer
 ])
 def test_full_size_self_selection(N, k, ties, n_audit):
     """T = S at full size.  Whole output: k distinct in-range indices per row.  Sampled rows (tile edges, first and
