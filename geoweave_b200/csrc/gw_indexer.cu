@@ -537,6 +537,7 @@ constexpr int kPlanSms = 148;  // SM count assumed when sizing the workspace (an
 
 struct WsLayout {
   size_t wsc, wtile, tau0, smax, tau_redo, flags, sample, list_cnt, cand, total;
+  size_t list_cnt_bytes, cand_bytes;
   int s_pad, m_pad, slots, caph, chunk_rows, nsplit, cap_split;
 };
 WsLayout ws_layout(int T, int S, int k) {
@@ -576,11 +577,13 @@ WsLayout ws_layout(int T, int S, int k) {
   L.nsplit = sp.step > 0 ? plan_splits(chunk_blocks, kPlanSms, (S + FBN - 1) / FBN) : 1;
   L.cap_split = L.nsplit == 1 ? L.caph : static_cast<int>(round_up(static_cast<size_t>(L.caph) * 5 / (4 * L.nsplit) + 2 * FBN, 64));
   const size_t fast_row_bytes = static_cast<size_t>(L.nsplit) * 2 * L.cap_split * 8;
-  L.list_cnt = take(static_cast<size_t>(L.chunk_rows) * L.nsplit * 2 * 4);
+  L.list_cnt_bytes = static_cast<size_t>(L.chunk_rows) * L.nsplit * 2 * 4;
+  L.list_cnt = take(L.list_cnt_bytes);
   L.sample = take(static_cast<size_t>(L.chunk_rows) * L.m_pad * 4);  // sampled scores of one chunk of rows
   const size_t robust_bytes = static_cast<size_t>(L.slots) * BM * robust_row_bytes;
   const size_t fast_bytes = static_cast<size_t>(L.chunk_rows) * fast_row_bytes;
-  L.cand = take(robust_bytes > fast_bytes ? robust_bytes : fast_bytes);
+  L.cand_bytes = robust_bytes > fast_bytes ? robust_bytes : fast_bytes;
+  L.cand = take(L.cand_bytes);
   L.total = off;
   return L;
 }
@@ -787,7 +790,21 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
                                                                                              tau0 + r0, smax + r0);
         GW_LAUNCH_CHECK();
       }
-      const int citems = cblocks * L.nsplit;
+      // a shorter last chunk gets a split count of its own (few row blocks on many SMs would otherwise run one
+      // full-length wave at low occupancy), provided its lists still fit the buffers sized for a full chunk
+      p.nsplit = L.nsplit;
+      p.caph = L.cap_split;
+      if (crows < L.chunk_rows) {
+        const int ns_try = plan_splits(cblocks, sms, (S + FBN - 1) / FBN);
+        const int cap_try =
+            ns_try == 1 ? L.caph : static_cast<int>(round_up(static_cast<size_t>(L.caph) * 5 / (4 * ns_try) + 2 * FBN, 64));
+        const size_t rows_pad = static_cast<size_t>(cblocks) * BM;
+        if (rows_pad * ns_try * 2 * cap_try * 8 <= L.cand_bytes && rows_pad * ns_try * 2 * 4 <= L.list_cnt_bytes) {
+          p.nsplit = ns_try;
+          p.caph = cap_try;
+        }
+      }
+      const int citems = cblocks * p.nsplit;
       rc = launch_indexer_fast(Hi, mq, mkf, p, idesc_fast, citems < sms ? citems : sms, st);
       if (rc != GW_OK) return rc;
       finalize_lists_kernel<<<(p.row_end - p.row_begin + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(p);
