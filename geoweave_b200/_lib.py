@@ -4,7 +4,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint, c_void_p, POINTER
 
 import torch
 
@@ -36,6 +36,9 @@ SIGNATURES = {
     "gw_strerror": (c_char_p, [c_int]),
     "gw_last_cuda_error": (c_int, []),
     "gw_abi_version": (c_int, []),
+    "gw_device_cache_reset": (c_int, []),
+    "gw_debug_bounded_wait_selftest": (c_int, [c_uint, c_void_p, c_void_p, c_void_p]),
+    "gw_debug_indexer_profile_enable": (c_int, [c_int]),
     "gw_indexer_topk_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "gw_debug_indexer_profile": (c_int, [c_void_p, c_int]),
     "gw_indexer_topk_launch_count": (c_int, [c_int, c_int, c_int, c_int]),
@@ -160,13 +163,21 @@ def debug_enabled() -> bool:
 
 
 def workspace(device, nbytes: int, tag: str = "indexer") -> torch.Tensor:
-    """A cached byte buffer of at least nbytes on `device` (grown on demand, never shrunk)."""
-    key = (torch.device(device).index, tag)
+    """A cached byte buffer of at least nbytes for (device, current stream) -- grown on demand, never shrunk.
+
+    The fused indexer's workspace holds thresholds, candidate lists and flags of the call in flight, so two calls
+    whose kernels may overlap must not share one: the cache is keyed by the stream the call is enqueued on.  A
+    buffer that is replaced by a larger one is handed back to the caching allocator on that same stream, which
+    orders its reuse behind the kernels already enqueued.  A captured CUDA graph must own its workspace instead
+    (``fused_score_topk(..., workspace=...)``): a cached buffer can be replaced after the capture.
+    """
+    dev = torch.device(device)
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream, tag)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = None
         _workspaces.pop(key, None)
-        buf = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        buf = None
+        buf = torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
         _workspaces[key] = buf
     return buf
 

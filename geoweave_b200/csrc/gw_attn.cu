@@ -309,7 +309,13 @@ int launch_attn(const AttnParams& p, cudaStream_t st) {
   constexpr int WARPS = W0 > 16 ? 16 : (W0 < 1 ? 1 : W0);
   constexpr size_t SMEM = static_cast<size_t>(WARPS) * NST * NTENS * SEG + static_cast<size_t>(WARPS) * NST * 8;
   auto kern = sparse_attn_kernel<T, D, G, WARPS, NST, MODE>;
-  GW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM)));
+  int dev = 0;
+  DeviceFacts facts;
+  int rc = device_facts(&dev, &facts);
+  if (rc != GW_OK) return rc;
+  static OncePerDevice smem_once;
+  rc = ensure_dynamic_smem(kern, SMEM, smem_once, dev);
+  if (rc != GW_OK) return rc;
   dim3 grid((p.T + WARPS - 1) / WARPS, p.H / G, p.B);
   kern<<<grid, WARPS * 32, SMEM, st>>>(p);
   GW_LAUNCH_CHECK();
@@ -385,9 +391,7 @@ extern "C" int gw_sparse_attn_fwd(const void* q, const void* k, const void* v, c
   p.kv_heads_contiguous = (k_strides[2] == D && v_strides[2] == D) ? 1 : 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // 16-bit token-major rows of up to 2 KB go to the tensor-core kernel, everything else to the scalar one
-  const char* force_scalar = getenv("GW_ATTN_SCALAR");
-  const bool use_mma = dtype != GW_F32 && D == 64 && (H == 8 || H == 16) && p.kv_heads_contiguous &&
-                       !(force_scalar && force_scalar[0] == '1');
+  const bool use_mma = dtype != GW_F32 && D == 64 && (H == 8 || H == 16) && p.kv_heads_contiguous;
   int rc;
   bool sum_done = false;
   if (use_mma) {

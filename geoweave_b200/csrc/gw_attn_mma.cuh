@@ -302,10 +302,14 @@ int launch_attn_mma(const AttnParams& p, cudaStream_t st) {
   constexpr size_t SMEM = static_cast<size_t>(SUM ? AM_NB_SUM : AM_NB) * 2 * AM_BATCH * (H * 64 * 2 + 16) +
                           (SUM ? static_cast<size_t>(H) * AM_SUM_MAXK * sizeof(float) : 0) + sizeof(AmShared);
   auto kern = sparse_attn_mma_kernel<T, HPW, SUM>;
-  GW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM)));
-  int dev = 0, sms = 0;
-  GW_CUDA_TRY(cudaGetDevice(&dev));
-  GW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int dev = 0;
+  DeviceFacts facts;
+  int rc = device_facts(&dev, &facts);
+  if (rc != GW_OK) return rc;
+  static OncePerDevice smem_once;
+  rc = ensure_dynamic_smem(kern, SMEM, smem_once, dev);
+  if (rc != GW_OK) return rc;
+  const int sms = facts.sms;
   const long long nq = static_cast<long long>(p.B) * p.T;
   const int grid = static_cast<int>(nq < sms ? nq : sms);
   kern<<<grid, AM_THREADS, SMEM, st>>>(p);

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/geoweave_b200.h"
 
 namespace gw {
@@ -27,6 +29,65 @@ inline int cuda_fail(cudaError_t e) {
   } while (0)
 
 #define GW_LAUNCH_CHECK() GW_CUDA_TRY(cudaGetLastError())
+
+// Per-device facts are read from the runtime once per device ordinal and kept for the life of the process
+// (gw_device_cache_reset forgets them, e.g. after a cudaDeviceReset).  A launch path pays for
+// cudaDeviceGetAttribute / cudaFuncSetAttribute only the first time it runs on a device.
+constexpr int kMaxDevices = 64;
+extern std::atomic<unsigned> g_cache_epoch;  // bumped by gw_device_cache_reset
+
+struct DeviceFacts {
+  int sms;
+  int cc_major;
+};
+struct DeviceFactsSlot {
+  std::atomic<unsigned> epoch_plus_one{0};  // 0 = never filled
+  DeviceFacts facts{0, 0};
+};
+extern DeviceFactsSlot g_device_facts[kMaxDevices];
+
+inline int device_facts(int* dev_out, DeviceFacts* out) {
+  int dev = 0;
+  GW_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return GW_ERR_UNSUPPORTED;
+  DeviceFactsSlot& slot = g_device_facts[dev];
+  const unsigned want = g_cache_epoch.load(std::memory_order_acquire) + 1u;
+  if (slot.epoch_plus_one.load(std::memory_order_acquire) != want) {
+    DeviceFacts f{0, 0};
+    GW_CUDA_TRY(cudaDeviceGetAttribute(&f.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    GW_CUDA_TRY(cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, dev));
+    slot.facts = f;  // racing first calls write the same values
+    slot.epoch_plus_one.store(want, std::memory_order_release);
+  }
+  if (dev_out) *dev_out = dev;
+  *out = slot.facts;
+  return GW_OK;
+}
+
+// "done once per device" marker for one kernel instantiation (one static object per launch site)
+struct OncePerDevice {
+  std::atomic<unsigned long long> mask{0};
+  std::atomic<unsigned> epoch{0};
+  bool needed(int dev) {
+    const unsigned e = g_cache_epoch.load(std::memory_order_acquire);
+    if (epoch.load(std::memory_order_acquire) != e) {
+      mask.store(0, std::memory_order_relaxed);
+      epoch.store(e, std::memory_order_release);
+    }
+    return ((mask.load(std::memory_order_acquire) >> dev) & 1ull) == 0;
+  }
+  void done(int dev) { mask.fetch_or(1ull << dev, std::memory_order_release); }
+};
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) the first time `kern` is launched on device `dev`
+template <typename Kern>
+inline int ensure_dynamic_smem(Kern kern, size_t bytes, OncePerDevice& once, int dev) {
+  if (once.needed(dev)) {
+    GW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+    once.done(dev);
+  }
+  return GW_OK;
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline size_t dtype_size(int dtype) { return dtype == GW_F32 ? 4 : 2; }
@@ -106,19 +167,21 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
-// Wait for a phase of an mbarrier, for at most ~2 s of wall time.  Returns false when the wait ran out;
+// Wait for a phase of an mbarrier, for at most `limit_ns` of wall time.  Returns false when the wait ran out;
 // the caller records GW_ERR_TIMEOUT in the status word and leaves its loop (no trap, no endless spin).
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
 }
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // ~2 s: every pipeline wait of the kernels
+constexpr unsigned long long kDrainLimitNs = 50000000ull;    // 50 ms: waiting for copies still in flight on the way out
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, kWaitLimitNs); }
 
 // 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier.  Both addresses 16-byte
 // aligned, size a multiple of 16.
@@ -135,6 +198,20 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// barrier `id` over `nthreads` threads that also ORs a predicate: every participant gets the same answer
+__device__ __forceinline__ bool named_bar_or(int id, int nthreads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
 }
 
 __device__ __forceinline__ void report_status(int* status_dev, int code) {

@@ -235,9 +235,10 @@ extern "C" int gw_project_epilogue(const void* fused, int dtype, int64_t tokens,
   p.table_rows = table_rows; p.qn_w = q_norm_w; p.qn_b = q_norm_b; p.kn_w = k_norm_w; p.kn_b = k_norm_b; p.in_w = idx_k_norm_w;
   p.in_b = idx_k_norm_b; p.qn_eps = q_norm_eps; p.kn_eps = k_norm_eps; p.in_eps = idx_k_norm_eps;
   p.q = q; p.k = k; p.v = v; p.q_idx = q_idx; p.k_idx = k_idx; p.w = w; p.status = status_dev;
-  int dev = 0, sms = 0;
-  GW_CUDA_TRY(cudaGetDevice(&dev));
-  GW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  DeviceFacts facts;
+  const int frc = device_facts(nullptr, &facts);
+  if (frc != GW_OK) return frc;
+  const int sms = facts.sms;
   const int64_t want = (tokens + FE_WARPS - 1) / FE_WARPS;
   const int64_t cap = static_cast<int64_t>(sms) * 8 * 4;  // a few waves of resident CTAs; warps walk tokens grid-stride
   const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);

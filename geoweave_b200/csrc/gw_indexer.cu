@@ -66,7 +66,7 @@ struct IdxParams {
                            // non-null: processes only the flagged blocks
   float* tau_redo;         // [T] fast kernel output: -inf for rows to redo, +inf for finished rows
   int* status;
-  int debug;               // timing experiments only (GW_IDX_DEBUG): 1 skip final select, 2 never append, 4 skip score math, 8 skip TMEM reads, 16 skip MMA
+  int profile;             // non-zero: the fast kernel fills its cycle counters (gw_debug_indexer_profile)
 };
 
 struct TwoSegSrc {
@@ -170,7 +170,13 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tma_load_2d(k_smem + (s * HI + h) * K_HEAD_BYTES, &tmK, h * DI, j * BN, &sh->k_full[s]);
         }
       }
-      if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
+      if (sh->abort_flag) {
+        // leaving early: let the copies this thread started land before the CTA's shared memory is given up
+        if (nblk > 0) mbar_wait_limit(&sh->q_full, (nblk - 1u) & 1u, kDrainLimitNs);
+        for (uint32_t u = kuse > NSTG ? kuse - NSTG : 0u; u < kuse; ++u)
+          mbar_wait_limit(&sh->k_full[u % NSTG], (u / NSTG) & 1u, kDrainLimitNs);
+        report_status(p.status, GW_ERR_TIMEOUT);
+      }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
@@ -189,7 +195,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (sh->abort_flag) break;
           tc_fence_after();
 #pragma unroll
-          for (int h = 0; h < HI && !(p.debug & 16); ++h) {
+          for (int h = 0; h < HI; ++h) {
             const uint64_t adesc = make_smem_desc(smem_u32(q_smem + h * Q_HEAD_BYTES));
             const uint64_t bdesc = make_smem_desc(smem_u32(k_smem + (s * HI + h) * K_HEAD_BYTES));
             const uint32_t d = tmem_base + b * ACC_COLS + h * BN;
@@ -235,16 +241,11 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int col_base = j * BN;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
-          if (p.debug & 8) break;
           uint32_t a[HI][16];
 #pragma unroll
           for (int h = 0; h < HI; ++h) tmem_ld_x16(taddr_row + h * BN + c0, a[h]);
           tmem_wait_ld();
           float sc[16];
-          if (p.debug & 4) {
-#pragma unroll
-            for (int c = 0; c < 16; ++c) sc[c] = __uint_as_float(a[0][c]);
-          } else
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
             const int col = col_base + c0 + c;
@@ -260,7 +261,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
               const int col = col_base + c0 + c;
-              if (sc[c] >= tau && col < p.S && !(p.debug & 2)) {
+              if (sc[c] >= tau && col < p.S) {
                 mybuf[cnt] = make_uint2(__float_as_uint(sc[c]), static_cast<uint32_t>(col));
                 ++cnt;
                 smin = fminf(smin, sc[c]);
@@ -323,7 +324,7 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int r = e; r < BM; r += EPI_WARPS) {
           const int n0 = sh->cnt[0][r], n1 = sh->cnt[1][r];
           const int grow = rb * BM + r;
-          if (n0 < 0 || grow >= p.T || sh->abort_flag || (p.debug & 1)) continue;
+          if (n0 < 0 || grow >= p.T || sh->abort_flag) continue;
           const int n = n0 + n1;
           const uint2* b0 = p.cand + ((static_cast<size_t>(blockIdx.x) * BM + r) * 2 + 0) * p.caph;
           const uint2* b1 = b0 + p.caph;
@@ -338,9 +339,12 @@ indexer_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           group_select_topk<32, SEL_BINS>(src, n, p.k, composite(score_key(lo_s), 0xffffffffu),
                                           composite(score_key(hi_s), 0u), sel[e], lane, 0, sink, nullptr);
         }
-        named_bar_sync(1, EPI_WARPS * 32);
+        // the eight warps must take the same way out: the flag is combined through the barrier itself, so a
+        // flag raised between two warps' reads cannot send one of them on to the next row block alone
+        if (named_bar_or(1, EPI_WARPS * 32, sh->abort_flag != 0)) break;
+      } else if (sh->abort_flag) {
+        break;  // score mode: the warps share no barrier, each may leave on its own
       }
-      if (sh->abort_flag) break;
     }
     if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
   }
@@ -385,8 +389,35 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// rows x (Hi*64) 16-bit matrix, row pitch `pitch_bytes`; box = 64 columns x box_rows, 128-byte swizzle
+// rows x (Hi*64) 16-bit matrix, row pitch `pitch_bytes`; box = 64 columns x box_rows, 128-byte swizzle.
+// An encoded map is a pure function of these arguments, so the last few are kept per host thread: a model that
+// calls the indexer layer after layer with the same buffers encodes each map once.
+struct MapKey {
+  const void* base;
+  int64_t rows, pitch;
+  int dtype, Hi, box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && pitch == o.pitch && dtype == o.dtype && Hi == o.Hi && box_rows == o.box_rows;
+  }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kMapCacheSize = 32;
+thread_local MapEntry g_map_cache[kMapCacheSize];
+
 int make_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, int Hi, int64_t pitch_bytes, int box_rows) {
+  const MapKey key{base, rows, pitch_bytes, dtype, Hi, box_rows};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 8;
+  h = (h ^ (static_cast<uint64_t>(rows) * 0x9E3779B97F4A7C15ull) ^ (static_cast<uint64_t>(pitch_bytes) << 7) ^
+       static_cast<uint64_t>(box_rows)) * 0xD6E8FEB86659FD93ull;
+  MapEntry& slot = g_map_cache[(h >> 32) % kMapCacheSize];
+  if (slot.valid && slot.key == key) {
+    *map = slot.map;
+    return GW_OK;
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return GW_ERR_CUDA;
   const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(Hi) * DI, static_cast<cuuint64_t>(rows)};
@@ -400,6 +431,9 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int64_t rows, int Hi
     g_last_cuda_error = static_cast<int>(r);
     return GW_ERR_CUDA;
   }
+  slot.key = key;
+  slot.map = *map;
+  slot.valid = true;
   return GW_OK;
 }
 
@@ -408,24 +442,30 @@ size_t smem_bytes(int Hi) {
          EPI_WARPS * sizeof(SelectSmem<SEL_BINS>) + sizeof(IdxShared);
 }
 
-int device_info(int* sms) {
-  int dev = 0, major = 0;
-  GW_CUDA_TRY(cudaGetDevice(&dev));
-  GW_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
-  GW_CUDA_TRY(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
-  return major == 10 ? GW_OK : GW_ERR_NO_SM100;
+int device_info(int* sms, int* dev) {
+  DeviceFacts f;
+  const int rc = device_facts(dev, &f);
+  if (rc != GW_OK) return rc;
+  *sms = f.sms;
+  return f.cc_major == 10 ? GW_OK : GW_ERR_NO_SM100;
 }
 
+// cycle counters of the fast kernel: off unless switched on through gw_debug_indexer_profile_enable
+std::atomic<int> g_profile_on{0};
+inline int profiling_enabled() { return g_profile_on.load(std::memory_order_relaxed); }
+
 template <int MODE>
-int launch_indexer(int Hi, const CUtensorMap& mq, const CUtensorMap& mk, const IdxParams& p, uint32_t idesc, int grid,
+int launch_indexer(int Hi, const CUtensorMap& mq, const CUtensorMap& mk, const IdxParams& p, uint32_t idesc, int grid, int dev,
                    cudaStream_t st) {
   const size_t smem = smem_bytes(Hi);
-#define GW_IDX_CASE(H)                                                                                          \
-  case H: {                                                                                                     \
-    auto kern = indexer_kernel<H, MODE>;                                                                        \
-    GW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))); \
-    kern<<<grid, NTHREADS, smem, st>>>(mq, mk, p, idesc);                                                       \
-    break;                                                                                                      \
+#define GW_IDX_CASE(H)                                                  \
+  case H: {                                                             \
+    auto kern = indexer_kernel<H, MODE>;                                \
+    static OncePerDevice once;                                          \
+    const int arc = ensure_dynamic_smem(kern, smem, once, dev);         \
+    if (arc != GW_OK) return arc;                                       \
+    kern<<<grid, NTHREADS, smem, st>>>(mq, mk, p, idesc);               \
+    break;                                                              \
   }
   switch (Hi) {
     GW_IDX_CASE(1)
@@ -440,14 +480,16 @@ int launch_indexer(int Hi, const CUtensorMap& mq, const CUtensorMap& mk, const I
 }
 
 int launch_indexer_fast(int Hi, const CUtensorMap& mq, const CUtensorMap& mk, const IdxParams& p, uint32_t idesc, int grid,
-                        cudaStream_t st) {
+                        int dev, cudaStream_t st) {
   const size_t smem = fast_smem_bytes(Hi);
-#define GW_IDXF_CASE(H)                                                                                         \
-  case H: {                                                                                                     \
-    auto kern = indexer_fast_kernel<H>;                                                                         \
-    GW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))); \
-    kern<<<grid, F_THREADS, smem, st>>>(mq, mk, p, idesc);                                                      \
-    break;                                                                                                      \
+#define GW_IDXF_CASE(H)                                                 \
+  case H: {                                                             \
+    auto kern = indexer_fast_kernel<H>;                                 \
+    static OncePerDevice once;                                          \
+    const int arc = ensure_dynamic_smem(kern, smem, once, dev);         \
+    if (arc != GW_OK) return arc;                                       \
+    kern<<<grid, F_THREADS, smem, st>>>(mq, mk, p, idesc);              \
+    break;                                                              \
   }
   switch (Hi) {
     GW_IDXF_CASE(1)
@@ -619,6 +661,11 @@ extern "C" int gw_debug_indexer_profile(unsigned long long* host_out, int max_en
   return n + 4;
 }
 
+extern "C" int gw_debug_indexer_profile_enable(int on) {
+  g_profile_on.store(on ? 1 : 0, std::memory_order_relaxed);
+  return GW_OK;
+}
+
 extern "C" int gw_indexer_topk_launch_count(int B, int T, int S, int k) {
   if (B <= 0 || T <= 0 || S <= 0 || k <= 0) return 0;
   // w scaling + fused pass, plus sampled scores + threshold pick + redo pass when sampling is on
@@ -637,8 +684,8 @@ extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const voi
   const int m = (S + key_step - 1) / key_step;
   if (out_row_stride < m) return GW_ERR_INVALID_ARG;
   if (T == 0) return GW_OK;
-  int sms = 0;
-  rc = device_info(&sms);
+  int sms = 0, dev = 0;
+  rc = device_info(&sms, &dev);
   if (rc != GW_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // this debug/verification entry owns a small scratch for w*scale (stream-ordered allocation)
@@ -668,7 +715,7 @@ extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const voi
     p.k = 0;
     p.key_step = key_step;
     p.status = status_dev;
-    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, BN), grid, st);
+    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, BN), grid, dev, st);
   }
   const cudaError_t fe = cudaFreeAsync(wsc, st);
   if (rc == GW_OK && fe != cudaSuccess) return cuda_fail(fe);
@@ -685,8 +732,8 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
   const WsLayout L = ws_layout(T, S, k);
   if (!workspace || workspace_bytes < L.total) return GW_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return GW_ERR_INVALID_ARG;
-  int sms = 0;
-  rc = device_info(&sms);
+  int sms = 0, dev = 0;
+  rc = device_info(&sms, &dev);
   if (rc != GW_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
@@ -732,13 +779,10 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     p.k = k;
     p.key_step = 1;
     p.status = status_dev;
-    {
-      const char* dbg = getenv("GW_IDX_DEBUG");
-      p.debug = dbg ? atoi(dbg) : 0;
-    }
+    p.profile = profiling_enabled();
     if (sp.step == 0) {
       // small key sets: the streaming kernel from tau = -inf
-      rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, p, idesc, grid, st);
+      rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, p, idesc, grid, dev, st);
       if (rc != GW_OK) return rc;
       continue;
     }
@@ -784,7 +828,7 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
         ps.row_begin = p.row_begin;
         ps.row_end = p.row_end;
         ps.status = status_dev;
-        rc = launch_indexer<MODE_SCORES>(Hi, mq, ms, ps, idesc, cblocks < grid ? cblocks : grid, st);
+        rc = launch_indexer<MODE_SCORES>(Hi, mq, ms, ps, idesc, cblocks < grid ? cblocks : grid, dev, st);
         if (rc != GW_OK) return rc;
         sample_threshold_kernel<<<(crows + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(sample, sp.m, L.m_pad, crows, sp.rank,
                                                                                              tau0 + r0, smax + r0);
@@ -805,7 +849,7 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
         }
       }
       const int citems = cblocks * p.nsplit;
-      rc = launch_indexer_fast(Hi, mq, mkf, p, idesc_fast, citems < sms ? citems : sms, st);
+      rc = launch_indexer_fast(Hi, mq, mkf, p, idesc_fast, citems < sms ? citems : sms, dev, st);
       if (rc != GW_OK) return rc;
       finalize_lists_kernel<<<(p.row_end - p.row_begin + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(p);
       GW_LAUNCH_CHECK();
@@ -820,8 +864,8 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     pr.caph = L.caph;
     pr.row_begin = 0;
     pr.row_end = 0;
-    pr.debug = 0;
-    rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, pr, idesc, grid, st);
+    pr.profile = 0;
+    rc = launch_indexer<MODE_TOPK>(Hi, mq, mk, pr, idesc, grid, dev, st);
     if (rc != GW_OK) return rc;
   }
   return GW_OK;
@@ -835,21 +879,24 @@ namespace {
 
 static __device__ __align__(256) float4 g_noalloc_wsc[GW_NOALLOC_MAX_KEYS];  // 4 MiB per GPU that loads the library
 
-constexpr int kMaxDevices = 64;
 float4* g_noalloc_ptr[kMaxDevices] = {};  // device address of the array above, per device (host code cannot use the symbol itself)
+unsigned g_noalloc_epoch[kMaxDevices] = {};  // value of g_cache_epoch + 1 when the address was looked up (0 = never)
 
 // Host code sees g_noalloc_wsc only as a stand-in symbol; the kernels need its device address, which differs per
-// device and is looked up once, with that device current.
+// device and is looked up once, with that device current (and again after gw_device_cache_reset).
 int noalloc_scratch(float4** out) {
   int dev = 0;
   GW_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return GW_ERR_UNSUPPORTED;
-  float4* ptr = __atomic_load_n(&g_noalloc_ptr[dev], __ATOMIC_ACQUIRE);
+  const unsigned want = g_cache_epoch.load(std::memory_order_acquire) + 1u;
+  float4* ptr = nullptr;
+  if (__atomic_load_n(&g_noalloc_epoch[dev], __ATOMIC_ACQUIRE) == want) ptr = __atomic_load_n(&g_noalloc_ptr[dev], __ATOMIC_RELAXED);
   if (ptr == nullptr) {
     void* addr = nullptr;
     GW_CUDA_TRY(cudaGetSymbolAddress(&addr, g_noalloc_wsc));
     ptr = static_cast<float4*>(addr);
-    __atomic_store_n(&g_noalloc_ptr[dev], ptr, __ATOMIC_RELEASE);  // racing first calls store the same value
+    __atomic_store_n(&g_noalloc_ptr[dev], ptr, __ATOMIC_RELAXED);  // racing first calls store the same value
+    __atomic_store_n(&g_noalloc_epoch[dev], want, __ATOMIC_RELEASE);
   }
   *out = ptr;
   return GW_OK;
@@ -869,8 +916,8 @@ extern "C" int gw_indexer_scores_noalloc(const void* q_idx, const void* k_idx, c
   const int64_t s_pad = static_cast<int64_t>(round_up(static_cast<size_t>(S), BN)) + static_cast<int64_t>(BN) * key_step + BN;
   if (s_pad > GW_NOALLOC_MAX_KEYS) return GW_ERR_TOO_LARGE;
   if (T == 0) return GW_OK;
-  int sms = 0;
-  rc = device_info(&sms);
+  int sms = 0, dev = 0;
+  rc = device_info(&sms, &dev);
   if (rc != GW_OK) return rc;
   float4* wsc = nullptr;
   rc = noalloc_scratch(&wsc);
@@ -900,7 +947,7 @@ extern "C" int gw_indexer_scores_noalloc(const void* q_idx, const void* k_idx, c
     p.k = 0;
     p.key_step = key_step;
     p.status = status_dev;
-    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, BN), grid, st);
+    rc = launch_indexer<MODE_SCORES>(Hi, mq, mk, p, make_idesc_mn(dtype == GW_BF16 ? 1 : 0, BM, BN), grid, dev, st);
     if (rc != GW_OK) return rc;
   }
   return GW_OK;

@@ -32,7 +32,7 @@ constexpr int WSLOTS = 8;                       // w*scale tile ring
 constexpr int W_TILE_FLOATS = 4 * FBN;          // [head][64] fp32
 constexpr int W_TILE_BYTES = W_TILE_FLOATS * 4; // 1 KB
 
-// Cycle counters for performance diagnosis (filled when bit 32 of IdxParams::debug is set, read back with
+// Cycle counters for performance diagnosis (filled when IdxParams::profile is set, read back with
 // gw_debug_indexer_profile): per CTA, per warp, eight 64-bit slots.
 constexpr int PROF_SLOTS = 8;
 __device__ unsigned long long g_idx_prof[MAX_SLOTS * (F_THREADS / 32) * PROF_SLOTS];  // [CTA][warp][slot]
@@ -218,7 +218,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 0) {
     // ------------------------------ TMA producer: Q block, key tiles, w*scale tiles ------------------------------
     if (lane == 0) {
-      ProfClock pc((p.debug & 32) != 0);
+      ProfClock pc(p.profile != 0);
       uint32_t tuse = 0, nblk = 0;
       for (int item = blockIdx.x; item < nitems && !sh->abort_flag; item += gridDim.x, ++nblk) {
         const int rb = blk_begin + item / nsplit, sp = item % nsplit;
@@ -257,7 +257,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // with one issuer committing every tile); a second issuer fills those gaps.
     const uint32_t b = (warp == 1) ? 0u : 1u;
     if (lane == 0) {
-      ProfClock pc((p.debug & 32) != 0);
+      ProfClock pc(p.profile != 0);
       uint32_t nblk = 0, use = 0, tbase = 0;
       const uint64_t adesc0 = make_smem_desc(smem_u32(q_smem));
       const uint64_t bdesc00 = make_smem_desc(smem_u32(k_smem));
@@ -280,14 +280,12 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (sh->abort_flag) break;
           tc_fence_after();
           const uint64_t bdesc0 = bdesc00 + s * ((HI * FK_HEAD_BYTES) >> 4);
-          if (!(p.debug & 16)) {
 #pragma unroll
-            for (int h = 0; h < HI; ++h)
+          for (int h = 0; h < HI; ++h)
 #pragma unroll
-              for (int kk = 0; kk < DI / 16; ++kk)  // +32 bytes along K per step = +2 in the address field
-                tc_mma_f16(d0 + h * FBN, adesc0 + h * (Q_HEAD_BYTES >> 4) + 2 * kk, bdesc0 + h * (FK_HEAD_BYTES >> 4) + 2 * kk, idesc,
-                           kk > 0 ? 1u : 0u);
-          }
+            for (int kk = 0; kk < DI / 16; ++kk)  // +32 bytes along K per step = +2 in the address field
+              tc_mma_f16(d0 + h * FBN, adesc0 + h * (Q_HEAD_BYTES >> 4) + 2 * kk, bdesc0 + h * (FK_HEAD_BYTES >> 4) + 2 * kk, idesc,
+                         kk > 0 ? 1u : 0u);
           tc_commit(&sh->k_empty[s]);
           tc_commit(&sh->acc_full[b]);
           pc.stop(3);
@@ -309,7 +307,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + strm * F_HALF;
     const bool last_partial = (p.S % FBN) != 0;
     uint32_t use0 = 0, use1 = 0, tbase = 0;
-    ProfClock pc((p.debug & 32) != 0);
+    ProfClock pc(p.profile != 0);
     for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
       const int rb = blk_begin + item / nsplit, sp = item % nsplit;
       const int t0 = sp * tps, t1 = (t0 + tps < ntiles) ? t0 + tps : ntiles;
@@ -434,7 +432,6 @@ __global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const Id
     return;
   }
   if (lane == 0) p.tau_redo[row] = INFINITY;
-  if (p.debug & 1) return;
   const uint2* b0 = p.cand + lrow * nseg * p.caph;
   IdxOutSink sink{p.out_idx + static_cast<int64_t>(row) * p.k,
                   p.out_scores ? static_cast<unsigned char*>(p.out_scores) +

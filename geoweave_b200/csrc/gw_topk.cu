@@ -9,6 +9,8 @@
 namespace gw {
 
 thread_local int g_last_cuda_error = 0;
+std::atomic<unsigned> g_cache_epoch{0};
+DeviceFactsSlot g_device_facts[kMaxDevices];
 
 namespace {
 
@@ -692,10 +694,15 @@ static int launch_topk_exact(const void* scores, int64_t rows, int64_t cols, int
       }
     }
     const size_t smem = row_bytes + cap + sizeof(RowSelSmem);
-    int dev = 0, sms = 0, per_sm = 0;
-    GW_CUDA_TRY(cudaGetDevice(&dev));
-    GW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    GW_CUDA_TRY(cudaFuncSetAttribute(topk_row_in_smem_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    int dev = 0, per_sm = 0;
+    DeviceFacts facts;
+    const int frc = device_facts(&dev, &facts);
+    if (frc != GW_OK) return frc;
+    const int sms = facts.sms;
+    // the shared-memory size depends on the row length, so the attribute is raised to the budget once per device
+    static OncePerDevice smem_once;
+    const int src = ensure_dynamic_smem(topk_row_in_smem_kernel<T>, kSmemBudget, smem_once, dev);
+    if (src != GW_OK) return src;
     GW_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, topk_row_in_smem_kernel<T>, kRowThreads, smem));
     if (per_sm >= 1) {
       const int64_t slots = static_cast<int64_t>(sms) * per_sm;
@@ -775,4 +782,8 @@ extern "C" const char* gw_strerror(int code) {
   }
 }
 extern "C" int gw_last_cuda_error(void) { return gw::g_last_cuda_error; }
-extern "C" int gw_abi_version(void) { return 1; }
+extern "C" int gw_abi_version(void) { return 2; }
+extern "C" int gw_device_cache_reset(void) {
+  gw::g_cache_epoch.fetch_add(1u, std::memory_order_acq_rel);
+  return GW_OK;
+}

@@ -18,7 +18,8 @@ import torch
 
 from .. import _lib
 
-__all__ = ["sparse_topk_indexer_func", "sparse_topk_indexer_inference_func", "indexer_scores", "clear_runtime_cache"]
+__all__ = ["sparse_topk_indexer_func", "sparse_topk_indexer_inference_func", "indexer_scores", "indexer_workspace_bytes",
+           "clear_runtime_cache"]
 
 clear_runtime_cache = _lib.clear_runtime_cache
 
@@ -40,9 +41,19 @@ def _check_qkw(q, k, w):
     return bq, tq, sk, hq, dq
 
 
+def indexer_workspace_bytes(B: int, T: int, S: int, Hi: int, Di: int, topk: int) -> int:
+    """Bytes of device workspace one ``fused_score_topk`` call of this shape needs."""
+    return int(_lib.load().gw_indexer_topk_workspace_bytes(B, T, S, Hi, Di, min(int(topk), S)))
+
+
 def fused_score_topk(q, k, w, topk: int, softmax_scale: Optional[float], return_scores: bool = True,
-                     out_indices: Optional[torch.Tensor] = None, out_scores: Optional[torch.Tensor] = None):
-    """q ``[B,T,Hi,Di]``, k ``[B,S,Hi,Di]``, w ``[B,S,Hi]`` -> (int32 ``[B,T,k]``, scores of q.dtype or None)."""
+                     out_indices: Optional[torch.Tensor] = None, out_scores: Optional[torch.Tensor] = None,
+                     workspace: Optional[torch.Tensor] = None):
+    """q ``[B,T,Hi,Di]``, k ``[B,S,Hi,Di]``, w ``[B,S,Hi]`` -> (int32 ``[B,T,k]``, scores of q.dtype or None).
+
+    ``workspace``: a uint8 tensor of at least ``indexer_workspace_bytes(...)`` that the caller owns (a captured CUDA
+    graph keeps its own, so that nothing can replace it between replays); by default a buffer cached per
+    (device, stream) is used.  Calls that may overlap on the GPU need different workspaces."""
     dev = _lib.require_cuda(q, k, w)
     B, T, S, Hi, Di = _check_qkw(q, k, w)
     q, k, w = q.contiguous(), k.contiguous(), w.contiguous()
@@ -61,7 +72,12 @@ def fused_score_topk(q, k, w, topk: int, softmax_scale: Optional[float], return_
         return idx, sc
     lib = _lib.load()
     nbytes = int(lib.gw_indexer_topk_workspace_bytes(B, T, S, Hi, Di, topk))
-    ws = _lib.workspace(dev, nbytes)
+    if workspace is None:
+        ws = _lib.workspace(dev, nbytes)
+    else:
+        ws = workspace
+        if ws.dtype != torch.uint8 or ws.device != dev or not ws.is_contiguous() or ws.numel() < nbytes:
+            raise ValueError(f"workspace must be a contiguous uint8 tensor of at least {nbytes} bytes on {dev}")
     with torch.cuda.device(dev):
         rc = lib.gw_indexer_topk_fused(q.data_ptr(), k.data_ptr(), w.data_ptr(), _lib.dtype_code(q), B, T, S, Hi, Di,
                                        scale, topk, idx.data_ptr(), _lib.ptr(sc), ws.data_ptr(), ws.numel(),

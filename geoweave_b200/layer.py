@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 from .custom_flash_attn.sparse_index_flash_attn import sparse_index_flash_attn_inference_func
-from .custom_indexer.sparse_topk_indexer import sparse_topk_indexer_inference_func
+from .custom_indexer.sparse_topk_indexer import fused_score_topk, indexer_workspace_bytes
 from .front_end import HEAD_DIM, FrontEndParams, project_qkv_and_indexer
 
 
@@ -38,11 +38,12 @@ class SparseGlobalAttentionLayer:
         self._graphs: Dict[tuple, dict] = {}
 
     # the chain itself: every call only enqueues on the current stream
-    def _chain(self, x, pos, reuse_idx):
+    def _chain(self, x, pos, reuse_idx, workspace=None):
         q, k, v, q_idx, k_idx, w = project_qkv_and_indexer(x, pos, self.params)
         if reuse_idx is None:
-            idx, _ = sparse_topk_indexer_inference_func(q_idx, k_idx, w, None, min(self.topk, x.shape[1]), self.idx_scale,
-                                                        return_scores=False)
+            with torch.inference_mode():
+                idx, _ = fused_score_topk(q_idx, k_idx, w, min(self.topk, x.shape[1]), self.idx_scale, return_scores=False,
+                                          workspace=workspace)
         else:
             idx = reuse_idx
         out, _ = sparse_index_flash_attn_inference_func(q, k, v, idx, None, False, self.attn_scale)
@@ -73,14 +74,20 @@ class SparseGlobalAttentionLayer:
 
     def _capture(self, x, pos, reuse_idx):
         st = {"x": x.clone(), "pos": None if pos is None else pos.to(torch.int64).clone(),
-              "idx_in": None if reuse_idx is None else reuse_idx.clone()}
+              "idx_in": None if reuse_idx is None else reuse_idx.clone(), "ws": None}
+        if reuse_idx is None:
+            # the graph records raw pointers, so it owns its indexer workspace: a buffer from the shared cache could
+            # be replaced (a larger shape, clear_runtime_cache) while the graph is still replayed
+            B, N = x.shape[:2]
+            nbytes = indexer_workspace_bytes(B, N, N, self.params.idx_heads, HEAD_DIM, min(self.topk, N))
+            st["ws"] = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
         side = torch.cuda.Stream(device=x.device)
         side.wait_stream(torch.cuda.current_stream(x.device))
-        with torch.cuda.stream(side):  # sizes the cached indexer workspace and moves parameters outside the capture
-            self._chain(st["x"], st["pos"], st["idx_in"])
+        with torch.cuda.stream(side):  # first-use set-up of the library and of torch happens outside the capture
+            self._chain(st["x"], st["pos"], st["idx_in"], st["ws"])
         torch.cuda.current_stream(x.device).wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            out, idx = self._chain(st["x"], st["pos"], st["idx_in"])
+            out, idx = self._chain(st["x"], st["pos"], st["idx_in"], st["ws"])
         st.update(graph=graph, out=out, idx=idx)
         return st

@@ -42,6 +42,20 @@ const char* gw_strerror(int code);
 int gw_last_cuda_error(void);   /* cudaError_t of the last GW_ERR_CUDA on this thread, else 0 */
 int gw_abi_version(void);
 
+/* The library remembers, per device ordinal, what it learned on its first call there: SM count, the raised
+ * shared-memory limits of its kernels, the device address of the no-allocation scratch array, and (per host
+ * thread) the last tensor maps it encoded.  A host that calls cudaDeviceReset, or destroys the context and
+ * makes a new one on the same ordinal, must call this afterwards; the next call on each device looks
+ * everything up again.  Host-only; no reference counterpart. */
+int gw_device_cache_reset(void);
+
+/* Diagnostics: a one-warp kernel waits on a barrier that nobody signals, for at most limit_us microseconds
+ * (1..100000), then writes GW_ERR_TIMEOUT to *status_dev and returns -- the way every wait inside this
+ * library's kernels ends when it cannot be satisfied.  waited_ns_dev (nullable) receives the time spent.
+ * The context stays usable.  No reference counterpart. */
+int gw_debug_bounded_wait_selftest(unsigned int limit_us, int* status_dev, unsigned long long* waited_ns_dev,
+                                   gw_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Stage 1+2 fused: indexer score + exact top-k, the N x N score matrix never reaches memory.
  *
@@ -64,11 +78,12 @@ int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const void* w, i
  * enough for the sampled threshold pass).  Host-only arithmetic; no reference counterpart. */
 int gw_indexer_topk_launch_count(int B, int T, int S, int k);
 
-/* Diagnostics: with the environment variable GW_IDX_DEBUG=32 the fused indexer kernel accumulates clock-cycle
- * counters per CTA and warp role (waiting on each hand-off, issuing, reducing, selecting).  This call copies
- * them to HOST memory (synchronising): four finalize counters (rows whose candidate lists overflowed, came up
+/* Diagnostics: after gw_debug_indexer_profile_enable(1) the fused indexer kernel accumulates clock-cycle
+ * counters per CTA and warp role (waiting on each hand-off, issuing, reducing, selecting); results are not
+ * affected.  gw_debug_indexer_profile copies them to HOST memory (synchronising): four finalize counters (rows whose candidate lists overflowed, came up
  * short, needed the general selection, were finished by the lean selection; reset by this call), then
  * [CTA][11 warps][8 slots] of 64-bit cycle counts; returns the number of entries copied or a negative status.  No reference counterpart. */
+int gw_debug_indexer_profile_enable(int on);
 int gw_debug_indexer_profile(unsigned long long* host_out, int max_entries);
 
 /* Dense score block (debug / verification / threshold sampling): out[t, j] = score[t, j*key_step] for
@@ -90,7 +105,8 @@ int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int d
  *
  * Limit: round_up(S, 64) + 64 * key_step + 64 <= GW_NOALLOC_MAX_KEYS, otherwise GW_ERR_TOO_LARGE and nothing
  * is launched.  The first call on each device looks up the array's device address (with that device
- * current); make that first call before any stream capture.  All calls on a device share the one array:
+ * current); make that first call before any stream capture.  The address is remembered per device ordinal:
+ * after cudaDeviceReset, or with a second context on the same device, call gw_device_cache_reset() first.  All calls on a device share the one array:
  * each call rewrites every entry it reads, so stale contents never matter, but two calls whose kernels may
  * overlap on the GPU (different streams) race on it -- serialise them. */
 #define GW_NOALLOC_MAX_KEYS 262144

@@ -168,3 +168,47 @@ def test_whole_layer_eager_graph_and_reused_indices():
         assert (out_rg.float() - out_e.float()).abs().max().item() <= 2e-2
     with pytest.raises(ValueError):
         eager(x, pos, reuse_topk_indices=idx_e[:, :10])
+    # the chain against the oracle, stage by stage on the chain's own intermediate tensors: the indices the layer
+    # returned are an exact top-k of the oracle's scores, and its output is the oracle's attention over them
+    from geoweave_b200.front_end import project_qkv_and_indexer
+
+    q, kk, v, qi, ki, w = [t.cpu() for t in project_qkv_and_indexer(x, pos, prm)]
+    rows = torch.arange(0, N, 61)
+    scores = orc.indexer_scores(qi[:, rows], ki, w, 0.125)
+    res = orc.audit_topk(idx_g[:, rows.to(dev())], scores, k, qi[:, rows], ki, w, 0.125)
+    assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
+    ref_out, _, _ = orc.sparse_attention(q[:, rows], kk, v, idx_g[:, rows.to(dev())].cpu(), 0.125)
+    got = out_g.view(1, N, heads, 64)[:, rows.to(dev())].float().cpu()
+    assert (got - ref_out).abs().max().item() <= 2e-2
+
+
+def test_a_captured_layer_survives_later_calls_that_replace_the_cached_workspace():
+    """A graph records raw pointers.  The layer's graph owns its indexer workspace, so a later, larger eager call
+    (which replaces the per-stream cached workspace) and clear_runtime_cache() cannot pull it from under a replay."""
+    import geoweave_b200
+    from geoweave_b200.front_end import FrontEndParams, rope_tables
+    from geoweave_b200.layer import SparseGlobalAttentionLayer
+
+    g = torch.Generator().manual_seed(33)
+    heads, dim, k = 16, 128, 128
+    width = 3 * heads * 64 + 2 * 4 * 64 + 4
+    weight = (torch.randn(width, dim, generator=g) * dim ** -0.5).bfloat16().to(dev())
+    cos, sin = rope_tables(40, dev(), torch.bfloat16)
+    prm = FrontEndParams(weight, None, heads, 4, None, None, None, cos, sin)
+    eager = SparseGlobalAttentionLayer(prm, k)
+    graphed = SparseGlobalAttentionLayer(prm, k, use_cuda_graph=True)
+    mk = lambda n: (torch.randn(1, n, dim, generator=g).bfloat16().to(dev()), torch.randint(0, 40, (1, n, 2), generator=g).to(dev()))
+    xa, pa = mk(5000)                      # shape A: large enough for the sampled fast path (lists in the workspace)
+    out_a, idx_a = [t.clone() for t in graphed(xa, pa)]
+    xb, pb = mk(9000)                      # a larger shape B through the shared cache, then the cache is dropped
+    eager(xb, pb)
+    geoweave_b200.clear_runtime_cache()
+    junk = [torch.full((1 << 24,), 0x7f, dtype=torch.uint8, device=dev()) for _ in range(8)]  # reuse freed blocks
+    xa2, pa2 = mk(5000)
+    out_r, idx_r = graphed(xa2, pa2)       # replay of A with new inputs
+    out_e, idx_e = eager(xa2, pa2)
+    geoweave_b200.check_status()
+    del junk
+    assert torch.equal(torch.sort(idx_r.long(), -1).values, torch.sort(idx_e.long(), -1).values)
+    assert (out_r.float() - out_e.float()).abs().max().item() <= 2e-2
+    assert not torch.equal(out_r, out_a)
