@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers per step (profiling)")
     ap.add_argument("--profile", action="store_true", help="profiling run: exact --warmup, no e2e pass, no CPU arm")
+    ap.add_argument("--no-extra-legs", action="store_true",
+                    help="skip the legs measured after the main region (attention in the HBM regime, the 256-view context, "
+                         "operator inputs from the reference's projections)")
     ap.add_argument("--micro", action="store_true",
                     help="instead of the path, time the stand-alone operators (exact top-k of materialised scores, merge of "
                          "two lists, scalar attention kernels) and print one JSON line with their roofline fractions")
@@ -66,8 +69,10 @@ def config_of(args, n_tokens, layers, desc, world):
 # CPU arm: the reference's torch-backend op sequence on a bounded sample of query rows
 # ---------------------------------------------------------------------------------------------------
 def cpu_reference_tokens_per_s(n_tokens, rows, repeats, seed=7):
-    from oracle import gw_oracle as orc
-
+    """Time the reference's CPU (`--device cpu --backend torch`) arithmetic of the path on `rows` query rows of one
+    layer with all keys resident.  With the staged copy of the reference present (baseline/_ref) its own functions
+    run -- LightningIndexer.select_topk_projected and DSAAttention._sparse_attention, fp32 (kind "reference");
+    otherwise the oracle's port of the same op sequence (kind "port")."""
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(seed)
@@ -78,16 +83,40 @@ def cpu_reference_tokens_per_s(n_tokens, rows, repeats, seed=7):
     k = torch.randn(1, H, n_tokens, D, generator=g)
     v = torch.randn(1, H, n_tokens, D, generator=g)
     rows = min(rows, n_tokens)
+    kind = "port"
+    try:
+        from baseline import ref_harness as rh
+
+        if rh.available():
+            rh.enable_import()
+            from easyvolcap.official_vggt.layers.dsa_attention import DSAAttention
+
+            attn = DSAAttention(H * D, num_heads=H, qk_norm=True, indexer_cfg=rh.indexer_cfg(TOPK, "torch")).eval()
+
+            def one(sl):
+                idx = attn.indexer.select_topk_projected(q_idx[:, sl], k_idx, w, topk=TOPK, return_scores=False)
+                attn._sparse_attention(q[:, :, sl], k, v, idx, None)
+
+            kind = "reference"
+    except Exception as exc:  # a broken staging area must not take the GPU arm's line with it
+        print(f"[bench] reference import failed, timing the port instead: {exc!r}", file=sys.stderr)
+    if kind == "port":
+        from oracle import gw_oracle as orc
+
+        def one(sl):
+            orc.reference_cpu_path(q_idx, k_idx, w, q, k, v, TOPK, DI ** -0.5, D ** -0.5, sl)
+
     times = []
     with torch.no_grad():
         for i in range(repeats + 1):
             lo = (i * rows) % max(1, n_tokens - rows + 1)
             t0 = time.perf_counter()
-            orc.reference_cpu_path(q_idx, k_idx, w, q, k, v, TOPK, DI ** -0.5, D ** -0.5, slice(lo, lo + rows))
+            one(slice(lo, lo + rows))
             times.append(time.perf_counter() - t0)
     times = times[1:] if len(times) > 1 else times  # first call warms the allocator
     per = statistics.median(times)
-    return rows / per, threads, per, f"{rows} query rows of one layer with all {n_tokens} keys resident, fp32, median of {len(times)}"
+    sample = f"{rows} query rows of one layer with all {n_tokens} keys resident, fp32, median of {len(times)}"
+    return rows / per, threads, per, sample, kind
 
 
 def run_reference(args):
@@ -97,16 +126,18 @@ def run_reference(args):
     views, tpv, layers, desc = WORKLOADS[args.workload]
     n_tokens = views * tpv
     t0 = time.perf_counter()
-    tps, threads, per, sample = cpu_reference_tokens_per_s(n_tokens, args.cpu_rows, max(1, args.steps))
+    tps, threads, per, sample, kind = cpu_reference_tokens_per_s(n_tokens, args.cpu_rows, max(1, args.steps))
     line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": n_tokens * layers / tps * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": config_of(args, n_tokens, layers, desc, 1),
-            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "note": "the reference is Python and is not present on the GPU box; this arm times a port of the op "
-                    "sequence its `--device cpu --backend torch` path executes (same ATen ops), all host threads; "
-                    "ms_per_step is extrapolated linearly in rows x layers",
+            "note": ("the reference's own LightningIndexer.select_topk_projected + DSAAttention._sparse_attention "
+                     "(its `--device cpu --backend torch` arithmetic) from the staged copy under baseline/_ref"
+                     if kind == "reference" else
+                     "no staged copy of the reference here: a port of the op sequence its `--device cpu --backend torch` "
+                     "path executes (same ATen ops)") + ", all host threads; ms_per_step is extrapolated linearly in rows x layers",
             "wall_s": time.perf_counter() - t0}
     print(json.dumps(line), flush=True)
 
@@ -187,7 +218,7 @@ def run_ours(args):
     from geoweave_b200 import _lib
     from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
     from geoweave_b200.custom_indexer import sparse_topk_indexer_inference_func
-    from geoweave_b200.sharding import gather_rows_packed, row_partition
+    from geoweave_b200.sharding import gather_rows_group, row_partition
 
     _lib.load()  # fail loudly if the CUDA library is missing: there is no other path
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -226,10 +257,12 @@ def run_ours(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     stage_events = []  # (start, after indexer, after attention) per layer call, only while timing
 
-    def layer_op(t, record):
+    last = {}          # tensors of the most recent recorded layer call (for the bare-gather ceiling)
+
+    def layer_op(t, record, n_tok=n_tokens, events=None):
         if world > 1:  # the indexer needs K_idx and w; K and V are gathered behind it
-            k_idx, w = [x.contiguous() for x in gather_rows_packed([t["k_idx"], t["w"]], n_tokens).result()]
-            kv_pend = gather_rows_packed([t["k"], t["v"]], n_tokens, async_op=True)
+            k_idx, w = [x.contiguous() for x in gather_rows_group([t["k_idx"], t["w"]], n_tok).result()]
+            kv_pend = gather_rows_group([t["k"], t["v"]], n_tok, async_op=True)
         else:
             k_idx, w, k, v = t["k_idx"], t["w"], t["k"], t["v"]
         if record:
@@ -243,7 +276,8 @@ def run_ours(args):
         out, _ = sparse_index_flash_attn_inference_func(t["q"], k, v, idx, None, False, D ** -0.5, False)
         if record:
             e2.record()
-            stage_events.append((e0, e1, e2))
+            (stage_events if events is None else events).append((e0, e1, e2))
+            last.update(idx=idx, k=k, v=v)
         return out
 
     def step_resident(record=False):
@@ -354,6 +388,109 @@ def run_ours(args):
     att_ms = statistics.mean(e1.elapsed_time(e2) for _, e1, e2 in stage_events)
     lib = _lib.load()
     launches = layers * (lib.gw_indexer_topk_launch_count(1, rows, n_tokens, TOPK) + 1)
+    es = 2
+
+    def attn_bytes_of(n_rows):
+        """Algorithmic bytes of one attention launch: gathered K and V rows, the index list, q and the output."""
+        return n_rows * (TOPK * 2 * H * D * es + TOPK * 4 + 2 * H * D * es)
+
+    def time_ms(fn, warm, reps):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    def bare_gather_ms(kk, vv, pos):
+        """The attention's bulk copies without its arithmetic, on the same index list (gw_debug_gather_rate)."""
+        T_, K_ = pos.shape[1], pos.shape[2]
+
+        def call():
+            _lib.check(lib.gw_debug_gather_rate(kk.data_ptr(), vv.data_ptr(), pos.data_ptr(), T_, kk.shape[1], K_, H * D * es,
+                                                kk.stride(1) * es, vv.stride(1) * es, _lib.status_word(dev).data_ptr(),
+                                                _lib.stream_ptr(dev)), "gw_debug_gather_rate")
+
+        return time_ms(call, 2, 3)
+
+    extra = not (args.no_extra_legs or args.profile)
+    # --- the ceiling of the gather method on the main workload's own index lists (L2-served at vggt32)
+    gather_ms = bare_gather_ms(last["k"], last["v"], last["idx"]) if extra and last else None
+    geoweave_b200.check_status()
+
+    # --- attention where HBM is the bound: uniformly random positions over the 256-view key set (K + V = 1.09 GB)
+    hbm_leg = None
+    if extra:
+        S_big, T_big = 256 * 1041, 8192
+        gg = torch.Generator(device=dev).manual_seed(99)
+        kb = torch.randn(1, S_big, H, D, device=dev, dtype=bf, generator=gg)
+        vb = torch.randn(1, S_big, H, D, device=dev, dtype=bf, generator=gg)
+        qb = torch.randn(1, T_big, H, D, device=dev, dtype=bf, generator=gg)
+        pb = torch.randint(0, S_big, (1, T_big, TOPK), device=dev, dtype=torch.int32, generator=gg)
+        ms_att = time_ms(lambda: sparse_index_flash_attn_inference_func(qb, kb, vb, pb, None, False, D ** -0.5, False), 3, 5)
+        ms_gat = bare_gather_ms(kb, vb, pb)
+        hbm_leg = {"ms": ms_att, "bytes": attn_bytes_of(T_big), "gather_ms": ms_gat, "queries": T_big, "keys": S_big}
+        del kb, vb, qb, pb
+        geoweave_b200.check_status()
+
+    # --- the 256-view context (one layer, N = 266496), sharded like the main workload: the 1 -> N curve of the long context
+    ctx = None
+    if extra and args.workload == "vggt32":
+        n_ctx = 256 * 1041
+        clo, chi = row_partition(n_ctx, world)[rank]
+        gg = torch.Generator(device=dev).manual_seed(4321 + rank)
+        mk = lambda *shape: torch.randn(*shape, device=dev, dtype=bf, generator=gg)
+        tc = {"q_idx": mk(1, chi - clo, HI, DI), "k_idx": mk(1, chi - clo, HI, DI),
+              "w": torch.rand(1, chi - clo, HI, device=dev, generator=gg).to(bf), "q": mk(1, chi - clo, H, D),
+              "k": mk(1, chi - clo, H, D), "v": mk(1, chi - clo, H, D)}
+        layer_op(tc, False, n_ctx)
+        geoweave_b200.check_status()
+        ctx_events = []
+        ctx_clocks = Clocks(local) if rank == 0 else None
+        t0c = time.perf_counter()
+        ms_ctx = timed(lambda: layer_op(tc, True, n_ctx, ctx_events), 2) / 2
+        ctx_clk = ctx_clocks.stop(t0c, time.perf_counter()) if ctx_clocks else None
+        ctx = {"ms": ms_ctx, "idx_ms": statistics.mean(a.elapsed_time(b) for a, b, _ in ctx_events),
+               "att_ms": statistics.mean(b.elapsed_time(c) for _, b, c in ctx_events), "rows": chi - clo, "tokens": n_ctx, "clocks": ctx_clk}
+        del tc
+        last.clear()
+        torch.cuda.empty_cache()
+        geoweave_b200.check_status()
+
+    # --- one vggt32 layer whose operator inputs come out of the reference's own projection modules (seeded weights)
+    proj = None
+    if extra and args.workload == "vggt32":
+        try:
+            from baseline import ref_harness as rh
+
+            if not rh.available():
+                proj = {"unavailable": "no staged copy of the reference (baseline/_ref)"}
+            else:
+                rh.enable_import()
+                blk = rh.build_block("vggt", TOPK, seed=0, device=dev, dtype=bf)
+                xin, pin = rh.make_inputs("vggt", views, seed=0, device=dev, dtype=bf)
+                with torch.no_grad():
+                    full = rh.operator_inputs(blk, blk.norm1(xin), pin)
+                tp = {n: x[:, lo:hi].contiguous() for n, x in zip(("q", "k", "v", "q_idx", "k_idx", "w"), full)}
+                del blk, xin, full
+                layer_op(tp, False)
+                pev = []
+                ms_p = timed(lambda: layer_op(tp, True, n_tokens, pev), 3) / 3
+                g_ms = bare_gather_ms(last["k"], last["v"], last["idx"])
+                proj = {"ms_per_layer": ms_p, "tokens_per_s": n_tokens / (ms_p * 1e-3),
+                        "idx_ms": statistics.mean(a.elapsed_time(b) for a, b, _ in pev),
+                        "att_ms": statistics.mean(b.elapsed_time(c) for _, b, c in pev), "bare_gather_ms": g_ms,
+                        "inputs": "q,k,v,q_idx,k_idx,w from the reference's DSABlock projections (qkv + q/k LayerNorm + rotary; "
+                                  "LightningIndexer.project) of ~N(0,1) tokens, trunc-normal(0.02) weights, w_proj bias 1"}
+                del tp
+                last.clear()
+                geoweave_b200.check_status()
+        except Exception as exc:
+            proj = {"unavailable": f"{type(exc).__name__}: {exc}"}
 
     if rank == 0:
         peaks = {}
@@ -363,18 +500,30 @@ def run_ours(args):
             pass
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         tc_peak = float(peaks.get("bf16_tflops", 1590.0))
+        tc_sustained = float(peaks.get("bf16_tflops_sustained", 1400.0))
         peak_src = "measured (MEASURED_PEAKS.json)" if peaks else "fallback"
-        es = 2
-        attn_bytes = rows * (TOPK * 2 * H * D * es + TOPK * 4 + 2 * H * D * es)
+        attn_bytes = attn_bytes_of(rows)
         attn_gbs = attn_bytes / (att_ms * 1e-3) / 1e9
-        # dram__bytes_read.sum + dram__bytes_write.sum of one sparse_attn_mma_kernel launch at N = 33312, k = 1024 (ncu,
-        # profiles/sparse_attn_mma_vggt32.md); scaled by the rows of this launch for the sharded runs
-        attn_traffic = (22.494e9 + 0.075e9) * rows / 33312 if (args.workload == "vggt32") else None
+        traffic = recorded_dram_traffic("sparse_attn_mma_kernel", args.workload, rows)
         idx_flops = 2.0 * rows * n_tokens * HI * DI
         idx_tfs = idx_flops / (idx_ms * 1e-3) / 1e12
         ms_step = ms_total / args.steps
         value = n_tokens * layers / (ms_step * 1e-3)
         e2e_value = n_tokens * layers / (ms_e2e / args.steps * 1e-3)
+        kv_mb = 2 * n_tokens * H * D * es / 1e6
+        roof = {"kernel": "sparse_attn_mma_kernel (stage 3 gather)", "bound": "hbm",
+                "regime": ("L2-served gather" if kv_mb < 400 else "HBM gather") + f": K+V of a layer = {kv_mb:.0f} MB against a 126 MB L2",
+                "achieved": attn_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": attn_gbs / hbm_peak, "traffic": traffic,
+                "dram_frac": (traffic / (att_ms * 1e-3) / 1e9 / hbm_peak) if traffic else None,
+                "peak_source": peak_src, "bytes_per_launch": attn_bytes, "ms_per_launch": att_ms,
+                "note": "achieved = ALGORITHMIC gather bytes / time.  When K+V of a layer fit (most of) the L2, the gather is served "
+                        "by the L2-to-SM path and this exceeds the HBM copy peak: frac is then not an HBM utilisation.  dram_frac = "
+                        "DRAM bytes of the launch (ncu capture of this kernel source, null if none is on record) / time / peak; "
+                        "gather_ceiling = the same bulk copies without any arithmetic on the same index lists, timed in this run; "
+                        "roofline_hbm = the same kernel where HBM does bind"}
+        if gather_ms:
+            roof["gather_ceiling"] = {"achieved": attn_bytes / (gather_ms * 1e-3) / 1e9, "unit": "GB/s", "ms": gather_ms,
+                                      "frac_of_ceiling": gather_ms / att_ms}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
                 "ms_per_step": ms_step, "ms_per_layer": ms_step / layers, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_of(args, n_tokens, layers, desc, world),
@@ -382,22 +531,66 @@ def run_ours(args):
                         "ms_per_step": ms_e2e / args.steps, "h2d_alone_gbs_rank0_clock": h2d_gbs, "host_binding": host_binding,
                         "host_enqueue_ms_per_step": (1e3 * statistics.median(enqueue_s)) if enqueue_s else None},
                 "gpu_launches": launches * args.steps,
-                "roofline": {"kernel": "sparse_attn_mma_kernel (stage 3 gather)", "bound": "hbm", "achieved": attn_gbs, "peak": hbm_peak,
-                             "unit": "GB/s", "frac": attn_gbs / hbm_peak, "traffic": attn_traffic, "peak_source": peak_src,
-                             "bytes_per_launch": attn_bytes, "ms_per_launch": att_ms,
-                             "note": "achieved = algorithmic gather bytes / time; K+V of a vggt32 layer (136 MB) are "
-                                     "mostly served from the 126 MB L2, so it can exceed the HBM copy peak; traffic = "
-                                     "DRAM bytes per launch from the ncu capture in profiles/"},
-                "roofline_indexer": {"kernel": "indexer_kernel (stage 1+2, all launches of one call)", "bound": "tensor",
+                "roofline": roof,
+                "roofline_indexer": {"kernel": "indexer kernels (stage 1+2, all launches of one call)", "bound": "tensor",
                                      "achieved": idx_tfs, "peak": tc_peak, "unit": "TFLOP/s", "frac": idx_tfs / tc_peak,
-                                     "flops_per_call": idx_flops, "ms_per_call": idx_ms, "peak_source": peak_src},
+                                     "frac_of_sustained": idx_tfs / tc_sustained, "flops_per_call": idx_flops,
+                                     "ms_per_call": idx_ms, "peak_source": peak_src},
                 "clocks": clk}
+        if hbm_leg:
+            gbs = hbm_leg["bytes"] / (hbm_leg["ms"] * 1e-3) / 1e9
+            line["roofline_hbm"] = {
+                "kernel": "sparse_attn_mma_kernel", "bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+                "frac": gbs / hbm_peak, "traffic": None, "peak_source": peak_src, "ms_per_launch": hbm_leg["ms"],
+                "bytes_per_launch": hbm_leg["bytes"],
+                "gather_ceiling": {"achieved": hbm_leg["bytes"] / (hbm_leg["gather_ms"] * 1e-3) / 1e9, "unit": "GB/s",
+                                   "ms": hbm_leg["gather_ms"], "frac_of_ceiling": hbm_leg["gather_ms"] / hbm_leg["ms"]},
+                "workload": f"{hbm_leg['queries']} queries, k = {TOPK}, positions uniformly random over {hbm_leg['keys']} keys "
+                            "(K + V = 1.09 GB, nine times the L2): every gathered row comes from DRAM; measured after the timed region"}
+        if ctx:
+            cf = 2.0 * ctx["rows"] * ctx["tokens"] * HI * DI
+            line["ctx256"] = {
+                "workload": "one VGGT-shaped layer over 256 views (N = 266496, k = 1024), query rows sharded like the main workload",
+                "ms_per_layer": ctx["ms"], "tokens_per_s": ctx["tokens"] / (ctx["ms"] * 1e-3), "indexer_ms": ctx["idx_ms"],
+                "attention_ms": ctx["att_ms"], "indexer_tflops": cf / (ctx["idx_ms"] * 1e-3) / 1e12,
+                "indexer_frac": cf / (ctx["idx_ms"] * 1e-3) / 1e12 / tc_peak,
+                "attention_gbs": attn_bytes_of(ctx["rows"]) / (ctx["att_ms"] * 1e-3) / 1e9, "steps": 2, "warmup": 1, "clocks": ctx["clocks"]}
+        if proj is not None:
+            if "ms_per_layer" in proj:
+                proj["indexer_frac"] = idx_flops / (proj["idx_ms"] * 1e-3) / 1e12 / tc_peak
+                proj["attention_gbs"] = attn_bytes / (proj["att_ms"] * 1e-3) / 1e9
+                proj["bare_gather_gbs"] = attn_bytes / (proj["bare_gather_ms"] * 1e-3) / 1e9
+            line["reference_projection_inputs"] = proj
         if world == 1 and not args.no_cpu_baseline and not args.profile:
-            tps, threads, per, sample = cpu_reference_tokens_per_s(n_tokens, args.cpu_rows, 2)
-            line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+            tps, threads, per, sample, kind = cpu_reference_tokens_per_s(n_tokens, args.cpu_rows, 2)
+            line["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+def kernel_source_digest(files=("gw_attn_mma.cuh", "gw_attn.cu", "gw_common.cuh")):
+    import hashlib
+
+    hsh = hashlib.sha256()
+    for name in files:
+        with open(os.path.join(ROOT, "geoweave_b200", "csrc", name), "rb") as f:
+            hsh.update(f.read())
+    return hsh.hexdigest()
+
+
+def recorded_dram_traffic(kernel, workload, rows):
+    """DRAM bytes (read + write) of one launch of `kernel` on `workload`, from an ncu capture recorded in
+    bench_traffic.json -- only if that capture was made of the kernel source as it is now (digest match);
+    scaled by the rows of this launch for a sharded run.  None otherwise."""
+    try:
+        rec = json.load(open(os.path.join(ROOT, "bench_traffic.json")))[kernel]
+    except Exception:
+        return None
+    if rec.get("workload") != workload or rec.get("source_sha256") != kernel_source_digest():
+        return None
+    return float(rec["dram_bytes_per_launch"]) * rows / float(rec["rows"])
 
 
 def run_micro(args):

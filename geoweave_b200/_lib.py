@@ -39,6 +39,7 @@ SIGNATURES = {
     "gw_device_cache_reset": (c_int, []),
     "gw_debug_bounded_wait_selftest": (c_int, [c_uint, c_void_p, c_void_p, c_void_p]),
     "gw_debug_indexer_profile_enable": (c_int, [c_int]),
+    "gw_debug_gather_rate": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p]),
     "gw_indexer_topk_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "gw_debug_indexer_profile": (c_int, [c_void_p, c_int]),
     "gw_indexer_topk_launch_count": (c_int, [c_int, c_int, c_int, c_int]),
@@ -46,6 +47,8 @@ SIGNATURES = {
                                       c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "gw_indexer_scores": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "gw_indexer_scores_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int64, c_int,
+                                      c_void_p, c_int64, c_void_p]),
     "gw_indexer_scores_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                           c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "gw_topk_exact": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -6,7 +6,8 @@ inference slot ``sparse_topk_indexer_inference_func`` the reference leaves open
 One fused tcgen05 kernel computes ``score[t,s] = sum_h w[s,h] * relu(scale * q[t,h].k[s,h])`` tile by tile and
 keeps the exact top-k per query in its epilogue; the score matrix is never written to memory.  The
 ``block_k`` / ``merge_blocks`` / ``outer_query_chunk`` arguments tune the reference's block-wise loop and have no
-meaning here; they are accepted and ignored.  ``mask`` and ``view_bias_data`` are not implemented (both
+meaning here; they are accepted and ignored.  fp32 operands (the reference's torch backend) take a plain fp32 score
+kernel followed by the exact top-k kernel instead.  ``mask`` and ``view_bias_data`` are not implemented (both
 published presets run without them) and raise ``NotImplementedError`` -- there is no fallback path.
 """
 from __future__ import annotations
@@ -35,10 +36,38 @@ def _check_qkw(q, k, w):
         raise ValueError("q/k/w shape mismatch")
     if not (q.dtype == k.dtype == w.dtype):
         raise TypeError("q/k/w must share one dtype")
-    if q.dtype not in (torch.bfloat16, torch.float16):
-        raise TypeError(f"the fused indexer takes bfloat16 or float16 inputs, got {q.dtype} "
+    if q.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise TypeError(f"the indexer takes bfloat16, float16 or float32 inputs, got {q.dtype} "
                         "(scores are always accumulated in fp32)")
     return bq, tq, sk, hq, dq
+
+
+_F32_SCORE_BYTES = 1 << 30  # fp32 operands: scores are materialised for this many bytes of query rows at a time
+
+
+def _score_topk_f32(q, k, w, topk, scale, idx, sc):
+    """fp32 operands (the reference's torch backend forces ``score_dtype=float32``, ``geoweave/inference.py:56-58``):
+    dense fp32 scores of a block of query rows from an FFMA kernel, then the exact top-k kernel on them, block after
+    block.  Far slower than the 16-bit tensor-core path and meant for the reference's small fp32 configuration."""
+    lib = _lib.load()
+    dev = q.device
+    B, T, Hi, Di = q.shape
+    S = k.shape[1]
+    if Di != 64:
+        raise _lib.GeoWeaveError(-2, "the indexer kernels are built for head_dim 64")
+    chunk = max(64, min(T, _F32_SCORE_BYTES // (4 * S * B)) // 64 * 64)
+    scratch = torch.empty(B * chunk * S, device=dev, dtype=torch.float32)
+    stream = _lib.stream_ptr(dev)
+    with torch.cuda.device(dev):
+        for r0 in range(0, T, chunk):
+            rows = min(chunk, T - r0)
+            _lib.check(lib.gw_indexer_scores_f32(q.data_ptr(), k.data_ptr(), w.data_ptr(), B, T, S, Hi, Di, scale, r0, rows,
+                                                 scratch.data_ptr(), S, stream), "gw_indexer_scores_f32")
+            for b in range(B):
+                rows_ptr = scratch.data_ptr() + 4 * b * rows * S
+                _lib.check(lib.gw_topk_exact(rows_ptr, _lib.GW_F32, rows, S, S, topk, idx[b, r0:r0 + rows].data_ptr(), None,
+                                             None if sc is None else sc[b, r0:r0 + rows].data_ptr(), stream), "gw_topk_exact")
+    return idx, sc
 
 
 def indexer_workspace_bytes(B: int, T: int, S: int, Hi: int, Di: int, topk: int) -> int:
@@ -70,6 +99,8 @@ def fused_score_topk(q, k, w, topk: int, softmax_scale: Optional[float], return_
         raise ValueError(f"out_scores must be a contiguous {q.dtype} [B,T,{topk}] tensor")
     if T == 0:
         return idx, sc
+    if q.dtype == torch.float32:
+        return _score_topk_f32(q, k, w, topk, scale, idx, sc)
     lib = _lib.load()
     nbytes = int(lib.gw_indexer_topk_workspace_bytes(B, T, S, Hi, Di, topk))
     if workspace is None:
@@ -98,6 +129,13 @@ def indexer_scores(q, k, w, softmax_scale: Optional[float] = None, key_step: int
     m = (S + key_step - 1) // key_step
     out = torch.empty((B, T, m), device=dev, dtype=torch.float32)
     lib = _lib.load()
+    if q.dtype == torch.float32:
+        if key_step != 1:
+            raise ValueError("key_step applies to the 16-bit tensor-core path only")
+        with torch.cuda.device(dev):
+            _lib.check(lib.gw_indexer_scores_f32(q.data_ptr(), k.data_ptr(), w.data_ptr(), B, T, S, Hi, Di, scale, 0, T,
+                                                 out.data_ptr(), S, _lib.stream_ptr(dev)), "gw_indexer_scores_f32")
+        return out
     with torch.cuda.device(dev):
         rc = lib.gw_indexer_scores(q.data_ptr(), k.data_ptr(), w.data_ptr(), _lib.dtype_code(q), B, T, S, Hi, Di, scale,
                                    int(key_step), out.data_ptr(), m, _lib.status_word(dev).data_ptr(),

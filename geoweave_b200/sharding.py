@@ -11,7 +11,8 @@ from typing import List, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["row_partition", "shard_rows", "gather_rows", "gather_rows_async", "gather_rows_packed", "sparse_global_attention_sharded"]
+__all__ = ["row_partition", "shard_rows", "gather_rows", "gather_rows_async", "gather_rows_packed", "gather_rows_group",
+           "sparse_global_attention_sharded"]
 
 
 def row_partition(n_rows: int, world_size: int) -> List[Tuple[int, int]]:
@@ -127,6 +128,43 @@ def gather_rows_packed(xs: Sequence[torch.Tensor], n_rows: int, group=None, asyn
     return _PendingPacked(pending, split)
 
 
+class _PendingGroup:
+    def __init__(self, work, outs):
+        self._work, self._outs = work, outs
+
+    def result(self):
+        if self._work is not None:
+            self._work.wait()
+            self._work = None
+        return self._outs
+
+
+def gather_rows_group(xs: Sequence[torch.Tensor], n_rows: int, group=None, async_op: bool = False):
+    """All-gather several row-sharded tensors ``[B, rows, ...]`` as ONE exchange step whose results are separate,
+    contiguous full tensors -- no packing copy in front and no un-packing copy behind.  With NCCL and equal shards the
+    all-gathers are issued as one coalesced group (one launch); batches larger than 1, ragged shards and other
+    back ends go through ``gather_rows_packed``.  ``result()`` returns the list of full tensors."""
+    xs = list(xs)
+    world = dist.get_world_size(group)
+    B, rows = xs[0].shape[:2]
+    equal = n_rows % world == 0 and rows * world == n_rows
+    if world == 1 or B != 1 or not equal or not all(x.is_cuda and x.is_contiguous() for x in xs):
+        if world > 1 and len({x.dtype for x in xs}) != 1:  # the packed form needs one dtype: gather one by one
+            return _PendingGroup(None, [gather_rows(x, n_rows, group) for x in xs])
+        return gather_rows_packed(xs, n_rows, group, async_op)
+    if any(x.shape[1] != rows for x in xs):
+        raise ValueError("gathered tensors must share the row count")
+    outs = [torch.empty((1, n_rows) + tuple(x.shape[2:]), dtype=x.dtype, device=x.device) for x in xs]
+    manager = getattr(dist, "_coalescing_manager", None)
+    if manager is None:
+        works = [dist.all_gather_into_tensor(o, x, group=group, async_op=async_op) for o, x in zip(outs, xs)]
+        return _PendingGroup(works[-1] if async_op else None, outs)  # one communication stream: the last one finishes last
+    with manager(group=group, async_ops=async_op) as cm:  # NCCL has a coalesced all-gather: one launch for the group
+        for o, x in zip(outs, xs):
+            dist.all_gather_into_tensor(o, x, group=group)
+    return _PendingGroup(cm if async_op else None, outs)
+
+
 def sparse_global_attention_sharded(q_idx, k_idx, w, q, k, v, topk: int, n_tokens: int, group=None,
                                     idx_scale=None, attn_scale=None, ops=None):
     """One layer of the path on this rank's token shard (all tensors ``[B, rows_of_this_rank, ...]``).
@@ -146,8 +184,8 @@ def sparse_global_attention_sharded(q_idx, k_idx, w, q, k, v, topk: int, n_token
             return sparse_index_flash_attn_inference_func(qq, kk_, vv, pos, None, False, sc, False)[0]
     else:
         indexer, attention = ops
-    k_idx_full, w_full = gather_rows_packed([k_idx, w], n_tokens, group).result()
-    kv_pending = gather_rows_packed([k, v], n_tokens, group, async_op=True)  # K and V arrive while the indexer runs
+    k_idx_full, w_full = gather_rows_group([k_idx, w], n_tokens, group).result()
+    kv_pending = gather_rows_group([k, v], n_tokens, group, async_op=True)  # K and V arrive while the indexer runs
     idx = indexer(q_idx, k_idx_full.contiguous(), w_full.contiguous(), topk, idx_scale)
     k_full, v_full = kv_pending.result()
     out = attention(q, k_full, v_full, idx, attn_scale)

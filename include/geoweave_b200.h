@@ -94,6 +94,15 @@ int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int d
                       int Di, float scale, int key_step, float* out, int64_t out_row_stride, int* status_dev,
                       gw_stream_t stream);
 
+/* Dense scores for fp32 operands (the arithmetic of the reference's `--backend torch` path, which forces
+ * score_dtype=float32: geoweave/inference.py:56-58, easyvolcap/official_vggt/layers/indexer.py:321-326, :430-466).
+ * q_idx [B,T,Hi,64], k_idx [B,S,Hi,64], w [B,S,Hi] fp32 contiguous; out[b, t - row_begin, s] for the query rows
+ * [row_begin, row_begin + rows) of every batch, fp32 [B, rows, out_row_stride].  A plain FFMA kernel (fp32 operands
+ * cannot use the 16-bit tensor-core path without changing the scores); the caller selects with gw_topk_exact. */
+int gw_indexer_scores_f32(const float* q_idx, const float* k_idx, const float* w, int B, int T, int S, int Hi, int Di,
+                          float scale, int64_t row_begin, int rows, float* out, int64_t out_row_stride,
+                          gw_stream_t stream);
+
 /* gw_indexer_scores for callers that must not allocate.  No counterpart in the reference.
  *
  * gw_indexer_scores needs a scratch table (w * scale as fp32, 16 bytes per key) and gets it from the stream-
@@ -178,6 +187,14 @@ int gw_project_epilogue(const void* fused, int dtype, int64_t tokens, int64_t ld
                         const float* k_norm_b, float k_norm_eps, const float* idx_k_norm_w, const float* idx_k_norm_b,
                         float idx_k_norm_eps, void* q, void* k, void* v, void* q_idx, void* k_idx, void* w,
                         int* status_dev, gw_stream_t stream);
+
+/* Diagnostics: the gather of gw_sparse_attn_fwd without its arithmetic -- for every query the K row and the V row
+ * (row_bytes <= 2048, a multiple of 16; rows k_row_stride_bytes / v_row_stride_bytes apart) of each valid entry of
+ * kv_pos int32 [T,K] is bulk-copied into shared memory and dropped.  Timed by the caller, it gives the rate this
+ * copy method reaches on that index list: the ceiling for the attention kernel on the same list (L2-to-SM path
+ * when K and V fit the L2, HBM otherwise).  Writes nothing to global memory.  No reference counterpart. */
+int gw_debug_gather_rate(const void* k, const void* v, const int32_t* kv_pos, int64_t T, int S, int K, int row_bytes,
+                         int64_t k_row_stride_bytes, int64_t v_row_stride_bytes, int* status_dev, gw_stream_t stream);
 
 #ifdef __cplusplus
 }

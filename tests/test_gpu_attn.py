@@ -2,6 +2,7 @@
 import pytest
 import torch
 
+import geoweave_b200
 from oracle import gw_oracle as orc
 from tests.gpu_util import dev, t
 
@@ -126,3 +127,21 @@ def test_attn_sum_with_padding_at_production_shapes(T, S, K, H, dtype):
     assert asum.dtype == torch.float32 and asum.shape == (1, T, K)
     assert (asum.cpu() - asum_ref).abs().max().item() <= 2e-3
     assert torch.equal(asum[0, 2].cpu(), torch.zeros(K)) and abs(float(asum[0, 3, 0]) - H) <= 1e-3
+
+
+def test_dense_index_entry_equals_plain_softmax_attention():
+    """dense_index_flash_attn_func (reference :3121): every key listed for every query = ordinary attention."""
+    from geoweave_b200.custom_flash_attn import dense_index_flash_attn_func
+
+    g = torch.Generator().manual_seed(77)
+    for dtype, tol, (T, S, Hh) in ((torch.bfloat16, 2e-2, (70, 333, 16)), (torch.float32, 1e-4, (33, 129, 4))):
+        q = torch.randn(2, T, Hh, 64, generator=g).to(dtype)
+        k = torch.randn(2, S, Hh, 64, generator=g).to(dtype)
+        v = torch.randn(2, S, Hh, 64, generator=g).to(dtype)
+        o, attn_sum = dense_index_flash_attn_func(q.to(dev()), k.to(dev()), v.to(dev()), None, False, 0.125)
+        geoweave_b200.check_status()
+        p = torch.softmax(torch.einsum("bthd,bshd->bhts", q.float(), k.float()) * 0.125, -1)
+        ref = torch.einsum("bhts,bshd->bthd", p, v.float())
+        assert o.shape == q.shape and o.dtype == dtype
+        assert (o.float().cpu() - ref).abs().max().item() <= tol
+        assert attn_sum.shape == (2, T, S) and (attn_sum.cpu() - p.sum(1)).abs().max().item() <= (4e-3 if dtype != torch.float32 else 1e-4)

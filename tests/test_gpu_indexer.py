@@ -158,9 +158,58 @@ def test_unsupported_arguments_fail_loudly():
     with pytest.raises(NotImplementedError):
         sparse_topk_indexer_func(q, kx, w, torch.zeros(1, 10, 40, device=dev()), 8, None, 0)
     with pytest.raises(TypeError):
-        sparse_topk_indexer_func(q.float(), kx.float(), w.float(), None, 8, None, 0)
+        sparse_topk_indexer_func(q.double(), kx.double(), w.double(), None, 8, None, 0)
+    with pytest.raises(TypeError):
+        sparse_topk_indexer_func(q.float(), kx, w, None, 8, None, 0)  # mixed dtypes
     sc, pos = score_topk_fused_select(q, kx, w, softmax_scale=0.125, out_pos=torch.empty(1, 10, 16, dtype=torch.int32, device=dev()))
     assert pos.shape == (1, 10, 16) and sc.shape == (1, 10, 16)
+
+
+def test_fp32_operands_small_cases_are_exact_on_integer_inputs():
+    """fp32 q_idx/k_idx/w (the reference's torch backend): FFMA score kernel + exact top-k kernel.  Integer-valued
+    inputs make every partial sum exact, so the selection must equal the oracle's bit for bit; ragged sizes."""
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_scores
+
+    for T, S, k, Hi in ((1, 64, 64, 4), (77, 130, 40, 3), (300, 5000, 512, 4), (65, 4097, 1024, 1)):
+        q, kx, w = make_indexer_inputs(T, S, Hi=Hi, seed=T + S, dtype=torch.float32, integer=True)
+        sc = indexer_scores(q.to(dev()), kx.to(dev()), w.to(dev()), 0.125)
+        ref_sc = orc.indexer_scores(q, kx, w, 0.125)
+        assert torch.equal(sc.cpu(), ref_sc), (T, S)
+        idx, top = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, k, 0.125, 256)
+        geoweave_b200.check_status()
+        assert idx.dtype == torch.int32 and top.dtype == torch.float32
+        assert torch.equal(sorted_idx(idx), orc.topk_tie_exact(ref_sc, k).long()), (T, S)
+        assert torch.equal(top.cpu(), ref_sc.gather(-1, idx.cpu().long()))
+    qa, ka, wa = make_indexer_inputs(70, 900, seed=71, dtype=torch.float32, integer=True)
+    qb, kb, wb = make_indexer_inputs(70, 900, seed=72, dtype=torch.float32, integer=True)
+    q, kx, w = torch.cat([qa, qb]), torch.cat([ka, kb]), torch.cat([wa, wb])
+    idx, _ = sparse_topk_indexer_func(q.to(dev()), kx.to(dev()), w.to(dev()), None, 100, 0.125, 256)
+    assert torch.equal(sorted_idx(idx), orc.topk_tie_exact(orc.indexer_scores(q, kx, w, 0.125), 100).long())
+
+
+def test_config1_in_fp32_end_to_end_at_full_size():
+    """The reference's CPU-runnable configuration as written: fp32, 4 views, N = 4164, 16 x 64 attention heads,
+    4 x 64 indexer heads, w ~ U(0,1), k = 1024.  Indices audited against the oracle on every row (an fp32 product
+    rounds, unlike a bf16 one, so the bound allows one more rounding per term); attention within 1e-4."""
+    from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+
+    N, k = 4164, 1024
+    g = torch.Generator().manual_seed(1235)
+    q, kk, v = [torch.randn(1, N, 16, 64, generator=g) for _ in range(3)]
+    q_idx, k_idx = torch.randn(1, N, 4, 64, generator=g), torch.randn(1, N, 4, 64, generator=g)
+    w = torch.rand(1, N, 4, generator=g)
+    idx, _ = sparse_topk_indexer_func(q_idx.to(dev()), k_idx.to(dev()), w.to(dev()), None, k, 0.125, 256)
+    out, _ = sparse_index_flash_attn_inference_func(q.to(dev()), kk.to(dev()), v.to(dev()), idx, None, False, 0.125, False)
+    geoweave_b200.check_status()
+    scores = orc.indexer_scores(q_idx, k_idx, w, 0.125)
+    res = orc.audit_topk(idx, scores, k, q_idx, k_idx, w, 0.125, c=130.0)
+    assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
+    assert res["rows_equal"] >= 0.98 * N, res
+    rows = torch.arange(0, N, 4)
+    ref, _, _ = orc.sparse_attention(q[:, rows], kk, v, idx[:, rows.to(dev())].cpu(), 0.125)
+    assert (out[:, rows.to(dev())].cpu() - ref).abs().max().item() <= 1e-4
 
 
 def _finalize_counters():
@@ -300,6 +349,71 @@ def test_full_size_self_selection(N, k, ties, n_audit):
         assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, (N, c0, res)
         swapped += res["swapped"]
     assert swapped <= 0.02 * rows.numel() * k, swapped
+
+
+def _device_inputs(T, S, seed, ties):
+    """bf16 q_idx [1,T,4,64], k_idx [1,S,4,64] ~N(0,1), w [1,S,4] ~U(0,1), made on the device; the tie variant overwrites
+    10 % of the key rows (k_idx AND w) by copies of random other rows."""
+    g = torch.Generator(device=dev()).manual_seed(seed)
+    q = torch.randn(1, T, 4, 64, device=dev(), generator=g).bfloat16()
+    kx = torch.randn(1, S, 4, 64, device=dev(), generator=g).bfloat16()
+    w = torch.rand(1, S, 4, device=dev(), generator=g).bfloat16()
+    if ties:
+        n_dup = S // 10
+        dst = torch.randperm(S, device=dev(), generator=g)[:n_dup]
+        src = torch.randint(0, S, (n_dup,), device=dev(), generator=g)
+        kx[0, dst] = kx[0, src]
+        w[0, dst] = w[0, src]
+    return q, kx, w
+
+
+@pytest.mark.parametrize("ties", [False, True])
+@pytest.mark.parametrize("k", [256, 512, 1024, 2048])
+@pytest.mark.parametrize("views", [8, 32, 128, 512])
+def test_config5_grid_same_scores_selection_is_bit_identical(views, k, ties):
+    """Every point of the sweep N = views x 1041, k in {256..2048}, with and without 10 % duplicated key rows: 256
+    query rows against all N keys.  The fused kernel's selection must equal, bit for bit, the exact top-k (ties to
+    the lower index) of the fp32 scores the same tensor-core main loop writes out densely."""
+    from geoweave_b200.custom_indexer import sparse_topk_indexer_func
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_scores
+
+    S, T = views * 1041, 256
+    q, kx, w = _device_inputs(T, S, seed=views * 10000 + k + int(ties), ties=ties)
+    dense = indexer_scores(q, kx, w, 0.125)
+    idx, sc = sparse_topk_indexer_func(q, kx, w, None, k, 0.125, 256)
+    geoweave_b200.check_status()
+    order = torch.sort(dense, dim=-1, descending=True, stable=True).indices[..., :k]
+    expect = torch.sort(order, dim=-1).values
+    got = torch.sort(idx.long(), dim=-1).values
+    assert torch.equal(got, expect), (views, k, ties, int((got != expect).any(-1).sum()))
+    assert torch.equal(sc.float(), dense.gather(-1, idx.long()).bfloat16().float())
+    if ties:  # the duplicates really produce ties at the boundary in some rows: the k-th and (k+1)-th score are equal
+        top = torch.sort(dense, dim=-1, descending=True).values
+        assert bool((top[..., k - 1] == top[..., k]).any())
+
+
+def test_score_topk_fused_select_returns_the_selected_scores_and_positions():
+    """The k = 512 wrapper of the reference (score_topk_fused_cuda.py:48-95), here for any k taken from the outputs."""
+    from geoweave_b200.custom_indexer.score_topk_fused_cuda import is_score_topk_fused_available, score_topk_fused_select
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_scores
+
+    assert is_score_topk_fused_available()
+    for T, S, K, ties in ((90, 3000, None, False), (200, 9000, 1024, True)):
+        q, kx, w = _device_inputs(T, S, seed=S, ties=ties)
+        dense = indexer_scores(q, kx, w, 0.125)
+        if K is None:
+            sc, pos = score_topk_fused_select(q, kx, w, softmax_scale=0.125)
+            K = 512  # the reference's fixed size
+        else:
+            out_pos = torch.full((1, T, K), -7, dtype=torch.int32, device=dev())
+            out_sc = torch.full((1, T, K), float("nan"), dtype=torch.bfloat16, device=dev())
+            sc, pos = score_topk_fused_select(q, kx, w, softmax_scale=0.125, out_scores=out_sc, out_pos=out_pos)
+            assert sc.data_ptr() == out_sc.data_ptr() and pos.data_ptr() == out_pos.data_ptr()
+        geoweave_b200.check_status()
+        assert tuple(pos.shape) == (1, T, K) and pos.dtype == torch.int32 and sc.dtype == q.dtype
+        order = torch.sort(dense, dim=-1, descending=True, stable=True).indices[..., :K]
+        assert torch.equal(torch.sort(pos.long(), -1).values, torch.sort(order, -1).values)
+        assert torch.equal(sc.float(), dense.gather(-1, pos.long()).bfloat16().float())
 
 
 def test_indexer_and_attention_replay_from_a_cuda_graph():

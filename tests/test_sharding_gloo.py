@@ -7,7 +7,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from geoweave_b200.sharding import gather_rows, gather_rows_packed, row_partition, shard_rows, sparse_global_attention_sharded
+from geoweave_b200.sharding import (gather_rows, gather_rows_group, gather_rows_packed, row_partition, shard_rows,
+                                    sparse_global_attention_sharded)
 
 
 def test_row_partition_covers_everything_once():
@@ -59,6 +60,11 @@ def _worker(rank, world, port, n_tokens, case, q):
             kk, vv = gather_rows_packed([mine["k"], mine["v"]], n_tokens, async_op=True).result()
             assert torch.equal(ki, full["k_idx"]) and torch.equal(ww, full["w"]) and ki.shape == full["k_idx"].shape
             assert torch.equal(kk, full["k"]) and torch.equal(vv, full["v"]) and kk.stride(-1) == 1
+            # the group form (one exchange step, separate results); tensors of different dtypes are gathered one by one
+            ki, ww = gather_rows_group([mine["k_idx"], mine["w"]], n_tokens).result()
+            kk, vv = gather_rows_group([mine["k"], mine["v"].double()], n_tokens, async_op=True).result()
+            assert torch.equal(ki, full["k_idx"]) and torch.equal(ww, full["w"])
+            assert torch.equal(kk, full["k"]) and torch.equal(vv, full["v"].double()) and vv.dtype == torch.float64
             q.put((rank, "ok"))
         elif case == "layer":
             out, idx = sparse_global_attention_sharded(mine["q_idx"], mine["k_idx"], mine["w"], mine["q"], mine["k"],
