@@ -60,7 +60,8 @@ struct IdxParams {
   int key_step;            // score mode: column j is key j * key_step
   const float* smax_in;    // [T] fast path: estimate of the row maximum (binning range of the final selection)
   int row_begin, row_end;  // fast path: rows of this launch (row_begin a multiple of the row block)
-  int* list_cnt;           // fast path: [rows of the launch][nsplit][2] list lengths (caph + 1 = overflowed)
+  int* list_cnt;           // fast path: [rows of the launch][nsplit][2 column halves] list lengths (caph + 1 = overflowed)
+  int* item_counter;       // fast path: work items handed out beyond the first one of every CTA (zero at launch)
   int nsplit;              // fast path: key splits per row block (lists and their capacity caph are per split)
   int* block_flags;        // [row blocks] fast kernel: sets 1 for blocks with a row to redo; robust kernel, when
                            // non-null: processes only the flagged blocks
@@ -577,8 +578,26 @@ int plan_splits(int blocks, int sms, int ntiles) {
 }
 constexpr int kPlanSms = 148;  // SM count assumed when sizing the workspace (any split count is valid on any device)
 
+// capacity of one fast-path list (row, key split, column group): its share of the row's expected candidates
+// (2 * caph covers the sampling scatter) with a quarter on top for the uneven spread over the lists, plus room
+// for the guard (a warp's 16 columns of a tile must always fit)
+int seg_capacity(int caph, int nsplit) {
+  return static_cast<int>(round_up(static_cast<size_t>(2) * caph * 5 / (4 * F_NQ * nsplit) + 4 * F_QCOLS, 32));
+}
+
+// The fast kernel moves only the low 32 bits of its list addresses, so no list may cross a 4 GiB boundary: when
+// such a boundary falls inside the list area, the area is shifted (by less than one list) so that the boundary
+// lies between two lists.  kListShiftSlack bytes are reserved behind the area for that.
+constexpr size_t kListShiftSlack = 1 << 20;
+uint2* place_lists(unsigned char* area, size_t area_bytes, size_t list_bytes) {
+  const uintptr_t base = reinterpret_cast<uintptr_t>(area);
+  const uintptr_t boundary = (base + 0xffffffffull) & ~static_cast<uintptr_t>(0xffffffffull);
+  if (boundary >= base + area_bytes + kListShiftSlack || list_bytes == 0 || list_bytes > kListShiftSlack) return reinterpret_cast<uint2*>(area);
+  return reinterpret_cast<uint2*>(area + (boundary - base) % list_bytes);
+}
+
 struct WsLayout {
-  size_t wsc, wtile, tau0, smax, tau_redo, flags, sample, list_cnt, cand, total;
+  size_t wsc, wtile, tau0, smax, tau_redo, flags, counter, sample, list_cnt, cand, total;
   size_t list_cnt_bytes, cand_bytes;
   int s_pad, m_pad, slots, caph, chunk_rows, nsplit, cap_split;
 };
@@ -603,6 +622,7 @@ WsLayout ws_layout(int T, int S, int k) {
   L.smax = take(static_cast<size_t>(T) * 4);
   L.tau_redo = take(static_cast<size_t>(T) * 4);
   L.flags = take(static_cast<size_t>(nblocks) * 4);
+  L.counter = take(256);
   // fast path: the lists of all rows of a launch are kept until the finalize kernel has run, so long inputs are
   // processed in chunks of whole waves of row blocks (about 2 GiB of lists per chunk)
   const size_t robust_row_bytes = static_cast<size_t>(2) * L.caph * 8;
@@ -617,15 +637,15 @@ WsLayout ws_layout(int T, int S, int k) {
   // key splits even out a launch with few row blocks or a ragged last wave; every split gets its own lists,
   // each with a 25 % larger share of the capacity than an even division would give
   L.nsplit = sp.step > 0 ? plan_splits(chunk_blocks, kPlanSms, (S + FBN - 1) / FBN) : 1;
-  L.cap_split = L.nsplit == 1 ? L.caph : static_cast<int>(round_up(static_cast<size_t>(L.caph) * 5 / (4 * L.nsplit) + 2 * FBN, 64));
-  const size_t fast_row_bytes = static_cast<size_t>(L.nsplit) * 2 * L.cap_split * 8;
-  L.list_cnt_bytes = static_cast<size_t>(L.chunk_rows) * L.nsplit * 2 * 4;
+  L.cap_split = seg_capacity(L.caph, L.nsplit);
+  const size_t fast_row_bytes = static_cast<size_t>(L.nsplit) * F_NQ * L.cap_split * 8;
+  L.list_cnt_bytes = static_cast<size_t>(L.chunk_rows) * L.nsplit * F_NQ * 4;
   L.list_cnt = take(L.list_cnt_bytes);
   L.sample = take(static_cast<size_t>(L.chunk_rows) * L.m_pad * 4);  // sampled scores of one chunk of rows
   const size_t robust_bytes = static_cast<size_t>(L.slots) * BM * robust_row_bytes;
   const size_t fast_bytes = static_cast<size_t>(L.chunk_rows) * fast_row_bytes;
   L.cand_bytes = robust_bytes > fast_bytes ? robust_bytes : fast_bytes;
-  L.cand = take(L.cand_bytes);
+  L.cand = take(L.cand_bytes + kListShiftSlack);
   L.total = off;
   return L;
 }
@@ -672,7 +692,7 @@ extern "C" int gw_indexer_topk_launch_count(int B, int T, int S, int k) {
   const WsLayout L = ws_layout(T, S, k);
   if (L.chunk_rows == 0) return B * 2;
   const int chunks = (T + L.chunk_rows - 1) / L.chunk_rows;
-  return B * (3 + 4 * chunks);  // 2 x w scaling, redo pass + (sampled scores, thresholds, filter, finalize) per chunk
+  return B * (3 + 4 * chunks);  // 2 x w scaling, redo pass + (sampled scores, thresholds, filter, finalize) per chunk; memsets not counted
 }
 
 extern "C" int gw_indexer_scores(const void* q_idx, const void* k_idx, const void* w, int dtype, int B, int T, int S,
@@ -792,6 +812,7 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     p.tau_redo = tau_redo;
     p.block_flags = flags;
     p.list_cnt = list_cnt;
+    p.item_counter = reinterpret_cast<int*>(ws + L.counter);
     p.wtile = wtile;
     p.nsplit = L.nsplit;
     p.caph = L.cap_split;
@@ -840,15 +861,16 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
       p.caph = L.cap_split;
       if (crows < L.chunk_rows) {
         const int ns_try = plan_splits(cblocks, sms, (S + FBN - 1) / FBN);
-        const int cap_try =
-            ns_try == 1 ? L.caph : static_cast<int>(round_up(static_cast<size_t>(L.caph) * 5 / (4 * ns_try) + 2 * FBN, 64));
+        const int cap_try = seg_capacity(L.caph, ns_try);
         const size_t rows_pad = static_cast<size_t>(cblocks) * BM;
-        if (rows_pad * ns_try * 2 * cap_try * 8 <= L.cand_bytes && rows_pad * ns_try * 2 * 4 <= L.list_cnt_bytes) {
+        if (rows_pad * ns_try * F_NQ * cap_try * 8 <= L.cand_bytes && rows_pad * ns_try * F_NQ * 4 <= L.list_cnt_bytes) {
           p.nsplit = ns_try;
           p.caph = cap_try;
         }
       }
       const int citems = cblocks * p.nsplit;
+      p.cand = place_lists(ws + L.cand, L.cand_bytes, static_cast<size_t>(p.caph) * 8);
+      GW_CUDA_TRY(cudaMemsetAsync(p.item_counter, 0, sizeof(int), st));
       rc = launch_indexer_fast(Hi, mq, mkf, p, idesc_fast, citems < sms ? citems : sms, dev, st);
       if (rc != GW_OK) return rc;
       finalize_lists_kernel<<<(p.row_end - p.row_begin + FIN_WARPS - 1) / FIN_WARPS, FIN_WARPS * 32, 0, st>>>(p);
@@ -860,6 +882,8 @@ extern "C" int gw_indexer_topk_fused(const void* q_idx, const void* k_idx, const
     pr.smax_in = nullptr;
     pr.tau_redo = nullptr;
     pr.list_cnt = nullptr;
+    pr.item_counter = nullptr;
+    pr.cand = cand;
     pr.nsplit = 1;
     pr.caph = L.caph;
     pr.row_begin = 0;

@@ -6,15 +6,30 @@
 // the Hi separate accumulators of a tile must fit twice into the 512 TMEM columns for the tensor cores to run
 // ahead of the epilogue, so N = 64 keys per tile with both operands in shared memory is the best available
 // point: 16 instructions = 768 cycles per 64-key tile, two thirds of the tensor peak.
-// The epilogue only filters: a thread appends (score, key) to its row's list in global memory when
-// score >= tau, through predicated stores at a moving offset (no divergent branch, no selection inside the
-// kernel).  TMEM reads are software-pipelined (the next 8 columns are in flight while 8 are reduced), the
-// head sum uses packed f32x2 arithmetic on column pairs, and the w*scale tile (stored head-major per tile)
-// comes from a small shared-memory ring that the TMA producer fills alongside the keys.  The lists of all rows of a launch stay in the workspace and a second,
-// occupancy-bound kernel (finalize_lists_kernel, one warp per row) turns each into the exact top-k.
-// A row whose list overflowed or holds fewer than k candidates is not resolved there: its row block is
-// flagged and the robust kernel redoes that block from tau = -inf.  The result is therefore exact for any
-// data; only the speed depends on the quality of tau.
+//
+// The epilogue only filters: a thread (= one query row) appends (score, key) to a list in global memory when
+// score >= tau, through predicated stores at a moving address (no divergent branch, no selection inside the
+// kernel).  It is bound by instruction issue -- about 16 issued instructions per score in the epilogue alone: four
+// FADD for 2*relu, two packed FMA, one shared-memory and half a tensor-memory load, and 6.6 for the compare, the
+// pairing of score and key index, the predicated store and its bump -- so everything that costs issue slots
+// without producing scores is kept out of the way: eight epilogue warps work on every tile (32 of its 64 columns
+// for 32 rows each, so the per-tile barrier traffic is paid once per 32 columns; sixteen warps of 16 columns and
+// two groups of eight on alternate tiles were both built and measured slower), TMEM reads are software-pipelined
+// (the next 8 columns are in flight while 8 are reduced), tensor-memory addresses stay in uniform registers (the
+// warp index is read through a shuffle, which the compiler treats as warp-uniform), and every wait of the
+// producer and MMA threads sleeps between polls instead of spinning on issue slots the epilogue warps need.  The w*scale tile (stored head-major per tile) comes from a small shared-memory ring
+// that the TMA producer fills alongside the keys.
+//
+// Work items are (row block, key split) pairs.  The first item of a CTA is its block index; every further item
+// is drawn from a global counter by the producer thread and handed to the other roles through shared memory
+// together with the query block's "loaded" barrier, so an SM that starts late or loses time (to a collective's
+// CTAs, say) simply takes fewer items.
+//
+// The lists of all rows of a launch stay in the workspace and a second, occupancy-bound kernel
+// (finalize_lists_kernel, one warp per row) turns each row's lists into the exact top-k.  A row whose list
+// overflowed or holds fewer than k candidates is not resolved there: its row block is flagged and the robust
+// kernel redoes that block from tau = -inf.  The result is therefore exact for any data; only the speed
+// depends on the quality of tau.
 #pragma once
 
 #include "gw_select_tight.cuh"
@@ -22,9 +37,11 @@
 namespace gw {
 namespace {
 
-constexpr int F_EPI = 8;                        // epilogue warps (2 streams x 4 lane quarters)
+constexpr int F_NQ = 2;                         // lists per (row, key split): one per column half of the tiles
+constexpr int F_EPI = 4 * F_NQ;                 // epilogue warps: 4 lane quarters x 2 column halves
 constexpr int F_THREADS = 64 + F_EPI * 32 + 32; // 352: producer, MMA issuer 0, 8 epilogue warps, MMA issuer 1
 constexpr int FBN = 64;                         // keys per tile
+constexpr int F_QCOLS = FBN / F_NQ;             // 32 columns per epilogue warp per tile
 constexpr int FNSTG = 3;                        // key-tile ring depth
 constexpr int FK_HEAD_BYTES = FBN * DI * 2;     // 8 KB
 constexpr int F_ACC_COLS = 256;                 // TMEM columns per accumulator set (Hi * 64 <= 256)
@@ -61,7 +78,25 @@ struct alignas(8) FastShared {
   uint64_t w_full[WSLOTS], w_empty[WSLOTS];
   uint32_t tmem_base;
   volatile int abort_flag;
+  volatile int item[2];        // work item of the n-th query block of this CTA at [n & 1]; -1 = no more work
 };
+
+// Wait used by the producer and the MMA threads, which are far ahead of the epilogue and wait most of the time:
+// between polls the thread sleeps, so its polling does not take issue slots from the epilogue warps that share
+// its scheduler.  A wake-up that comes a few hundred cycles late is absorbed by the two accumulator sets and
+// the three key stages.  Bounded like every other wait.
+__device__ __forceinline__ bool mbar_wait_sleeping(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait_hint(bar, parity, 4000u)) return true;  // suspended in hardware until the phase completes or ~4 us pass
+      __nanosleep(128);
+    }
+    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+  }
+}
 
 // packed fp32 pairs (sm_100 f32x2 pipe): d = a * b + c on both halves
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
@@ -94,36 +129,43 @@ __device__ __forceinline__ void fast_load_chunk(uint32_t taddr, uint32_t (&a)[HI
   for (int h = 0; h < HI; ++h) tmem_ld_x8(taddr + h * FBN, a[h]);
 }
 
-// Append (score, col) at *wp and advance wp when score >= tau (and col < S if GUARD): compare, predicated store and
-// predicated pointer bump in one block, so an append costs four instructions and never a branch.
+// Append (score, col) at the list position {lo, hi} (the two halves of a 64-bit address) and advance it when
+// score >= tau (and col < S if GUARD).  Only the low half ever moves -- the host lays the lists out so that none
+// crosses a 4 GiB boundary -- which makes the bump one predicated 32-bit add: compare, predicated store,
+// predicated add, no branch and no carry chain (the cheapest of the forms measured: 6.6 issued instructions per
+// column including the pairing of score and key index, against 7.8 to 8.8 for 64-bit or counter-based forms).
 template <bool GUARD>
-__device__ __forceinline__ void append_if(uint2*& wp, float s, float tau, uint32_t col, int S) {
+__device__ __forceinline__ void append_if(uint32_t& lo, uint32_t hi, float s, float tau, uint32_t col, int S) {
   if (GUARD) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ge.f32 p, %1, %2;\n\t"
-        "setp.lt.and.s32 p, %4, %5, p;\n\t"
-        "@p st.global.v2.b32 [%0], {%3, %4};\n\t"
-        "@p add.u64 %0, %0, 8;\n\t}"
-        : "+l"(wp)
-        : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col), "r"(S));
+        "{\n\t.reg .pred p;\n\t.reg .b64 a;\n\t"
+        "mov.b64 a, {%0, %1};\n\t"
+        "setp.ge.f32 p, %2, %3;\n\t"
+        "setp.lt.and.s32 p, %5, %6, p;\n\t"
+        "@p st.global.v2.b32 [a], {%4, %5};\n\t"
+        "@p add.u32 %0, %0, 8;\n\t}"
+        : "+r"(lo)
+        : "r"(hi), "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col), "r"(S)
+        : "memory");
   } else {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ge.f32 p, %1, %2;\n\t"
-        "@p st.global.v2.b32 [%0], {%3, %4};\n\t"
-        "@p add.u64 %0, %0, 8;\n\t}"
-        : "+l"(wp)
-        : "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col));
+        "{\n\t.reg .pred p;\n\t.reg .b64 a;\n\t"
+        "mov.b64 a, {%0, %1};\n\t"
+        "setp.ge.f32 p, %2, %3;\n\t"
+        "@p st.global.v2.b32 [a], {%4, %5};\n\t"
+        "@p add.u32 %0, %0, 8;\n\t}"
+        : "+r"(lo)
+        : "r"(hi), "f"(s), "f"(tau), "r"(__float_as_uint(s)), "r"(col)
+        : "memory");
   }
 }
 
 // Reduce 8 columns held in `a` and append the ones that pass.  wt = this tile's w*scale, [head][FBN]; c0 = first
 // column within the tile; col_g = its global key index.  All loads and arithmetic come first; the appends
-// are predicated stores at a moving 32-bit offset.  The caller guarantees room for 8 more entries.
+// are predicated stores at a moving address.  The caller guarantees room for 8 more entries.
 template <int HI, bool GUARD>
 __device__ __forceinline__ void fast_reduce_chunk(const uint32_t (&a)[HI][8], const float* __restrict__ wt, int c0, int col_g,
-                                                  int S, float tau, uint2*& wp) {
+                                                  int S, float tau, uint32_t& lo, uint32_t hi) {
   float2 acc[4];
 #pragma unroll
   for (int h = 0; h < HI; ++h) {
@@ -147,27 +189,34 @@ __device__ __forceinline__ void fast_reduce_chunk(const uint32_t (&a)[HI][8], co
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     const float s = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
-    append_if<GUARD>(wp, s, tau, static_cast<uint32_t>(col_g + c), S);
+    append_if<GUARD>(lo, hi, s, tau, static_cast<uint32_t>(col_g + c), S);
   }
 }
 
-// One warp's half of a tile: columns c_begin .. c_begin + 31 (taddr already points at column c_begin of head 0)
-constexpr int F_HALF = FBN / 2;
+// One warp's share of a tile: columns c_begin .. c_begin + 31 (taddr already points at column c_begin of head 0).
+// With two epilogue warps per scheduler the TMEM round trip is hidden by software pipelining: the next 8 columns
+// are in flight while 8 are reduced.
 template <int HI, bool GUARD>
 __device__ __forceinline__ void fast_reduce_tile(uint32_t taddr, const float* wt, int c_begin, int col_base, int S, float tau,
-                                                 uint2*& wp) {
+                                                 uint32_t& lo, uint32_t hi) {
   uint32_t a0[HI][8], a1[HI][8];
   fast_load_chunk<HI>(taddr, a0);
   tmem_wait_ld();
 #pragma unroll
-  for (int ch = 0; ch < F_HALF / 8; ch += 2) {
+  for (int ch = 0; ch < F_QCOLS / 8; ch += 2) {
     fast_load_chunk<HI>(taddr + (ch + 1) * 8, a1);  // in flight while a0 is reduced
-    fast_reduce_chunk<HI, GUARD>(a0, wt, c_begin + ch * 8, col_base + c_begin + ch * 8, S, tau, wp);
+    fast_reduce_chunk<HI, GUARD>(a0, wt, c_begin + ch * 8, col_base + c_begin + ch * 8, S, tau, lo, hi);
     tmem_wait_ld();
-    if (ch + 2 < F_HALF / 8) fast_load_chunk<HI>(taddr + (ch + 2) * 8, a0);
-    fast_reduce_chunk<HI, GUARD>(a1, wt, c_begin + (ch + 1) * 8, col_base + c_begin + (ch + 1) * 8, S, tau, wp);
-    if (ch + 2 < F_HALF / 8) tmem_wait_ld();
+    if (ch + 2 < F_QCOLS / 8) fast_load_chunk<HI>(taddr + (ch + 2) * 8, a0);
+    fast_reduce_chunk<HI, GUARD>(a1, wt, c_begin + (ch + 1) * 8, col_base + c_begin + (ch + 1) * 8, S, tau, lo, hi);
+    if (ch + 2 < F_QCOLS / 8) tmem_wait_ld();
   }
+}
+
+// key tiles [t0, t1) of split `sp`: an even division, so no split is empty while nsplit <= ntiles
+__device__ __forceinline__ void split_range(int sp, int nsplit, int ntiles, int& t0, int& t1) {
+  t0 = static_cast<int>(static_cast<long long>(sp) * ntiles / nsplit);
+  t1 = static_cast<int>(static_cast<long long>(sp + 1) * ntiles / nsplit);
 }
 
 template <int HI>
@@ -177,17 +226,19 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* q_smem = smem;                                  // HI x 16 KB, 128-byte swizzled rows
-  unsigned char* k_smem = q_smem + HI * Q_HEAD_BYTES;            // FNSTG x HI x 6 KB
+  unsigned char* k_smem = q_smem + HI * Q_HEAD_BYTES;            // FNSTG x HI x 8 KB
   float* w_smem = reinterpret_cast<float*>(k_smem + FNSTG * HI * FK_HEAD_BYTES);
   FastShared* sh = reinterpret_cast<FastShared*>(reinterpret_cast<unsigned char*>(w_smem) + WSLOTS * W_TILE_BYTES);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // read through a shuffle, the warp index is warp-uniform for the compiler: role dispatch and every
+  // tensor-memory address derived from it stay in uniform registers
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
   const int blk_begin = p.row_begin / BM, blk_end = (p.row_end + BM - 1) / BM;  // this launch's row blocks
   const int ntiles = (p.S + FBN - 1) / FBN;
   // work item = (row block, key split): a launch with fewer row blocks than SMs, or a ragged last wave, is
   // evened out by cutting the key range of every row block into nsplit pieces that go to different CTAs
   const int nsplit = p.nsplit;
-  const int tps = (ntiles + nsplit - 1) / nsplit;  // key tiles per split
   const int nitems = (blk_end - blk_begin) * nsplit;
 
   if (threadIdx.x == 0) {
@@ -206,6 +257,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&sh->w_empty[s], F_EPI);
     }
     sh->abort_flag = 0;
+    sh->item[0] = sh->item[1] = -1;
     mbar_fence_init();
     fence_proxy_async_smem();
   }
@@ -213,19 +265,28 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = sh->tmem_base;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, sh->tmem_base, 0);  // warp-uniform for the compiler, like `warp`
 
   if (warp == 0) {
-    // ------------------------------ TMA producer: Q block, key tiles, w*scale tiles ------------------------------
+    // ------------------------------ TMA producer: work items, Q block, key tiles, w*scale tiles ------------------------------
     if (lane == 0) {
       ProfClock pc(p.profile != 0);
       uint32_t tuse = 0, nblk = 0;
-      for (int item = blockIdx.x; item < nitems && !sh->abort_flag; item += gridDim.x, ++nblk) {
-        const int rb = blk_begin + item / nsplit, sp = item % nsplit;
-        const int t0 = sp * tps, t1 = (t0 + tps < ntiles) ? t0 + tps : ntiles;
+      int item = blockIdx.x;
+      for (;; ++nblk) {
+        if (item >= nitems) item = -1;
         pc.start();
-        if (!mbar_wait_bounded(&sh->q_empty, (nblk & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+        if (!mbar_wait_sleeping(&sh->q_empty, (nblk & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
         pc.stop(0);
+        if (sh->abort_flag) break;
+        sh->item[nblk & 1u] = item;  // made visible to the other roles by the arrival on q_full below
+        if (item < 0) {
+          mbar_arrive(&sh->q_full);
+          break;
+        }
+        const int rb = blk_begin + item / nsplit, sp = item % nsplit;
+        int t0, t1;
+        split_range(sp, nsplit, ntiles, t0, t1);
         mbar_arrive_expect_tx(&sh->q_full, HI * Q_HEAD_BYTES);
 #pragma unroll
         for (int h = 0; h < HI; ++h) tma_load_2d(q_smem + h * Q_HEAD_BYTES, &tmQ, h * DI, rb * BM, &sh->q_full);
@@ -233,9 +294,9 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const uint32_t s = tuse % FNSTG, n = tuse / FNSTG;
           const uint32_t ws = tuse % WSLOTS, wn = tuse / WSLOTS;
           pc.start();
-          if (!mbar_wait_bounded(&sh->k_empty[s], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_sleeping(&sh->k_empty[s], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
           pc.stop(1);
-          if (!mbar_wait_bounded(&sh->w_empty[ws], (wn & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_sleeping(&sh->w_empty[ws], (wn & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
           pc.stop(2);
           if (sh->abort_flag) break;
           mbar_arrive_expect_tx(&sh->w_full[ws], W_TILE_BYTES);
@@ -246,9 +307,20 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tma_load_2d(k_smem + (s * HI + h) * FK_HEAD_BYTES, &tmK, h * DI, j * FBN, &sh->k_full[s]);
           pc.stop(3);
         }
+        if (sh->abort_flag) break;
+        item = static_cast<int>(gridDim.x) + atomicAdd(p.item_counter, 1);
       }
       pc.flush(warp);
-      if (sh->abort_flag) report_status(p.status, GW_ERR_TIMEOUT);
+      if (sh->abort_flag) {
+        // leaving early: let the copies this thread started land before the CTA's shared memory is given up,
+        // and release the roles that may still be waiting for a work item
+        if (nblk > 0) mbar_wait_limit(&sh->q_full, (nblk - 1u) & 1u, kDrainLimitNs);
+        for (uint32_t u = tuse > FNSTG ? tuse - FNSTG : 0u; u < tuse; ++u)
+          mbar_wait_limit(&sh->k_full[u % FNSTG], (u / FNSTG) & 1u, kDrainLimitNs);
+        for (uint32_t u = tuse > WSLOTS ? tuse - WSLOTS : 0u; u < tuse; ++u)
+          mbar_wait_limit(&sh->w_full[u % WSLOTS], (u / WSLOTS) & 1u, kDrainLimitNs);
+        report_status(p.status, GW_ERR_TIMEOUT);
+      }
     }
   } else if (warp == 1 || warp == 2 + F_EPI) {
     // ------------------------------ MMA issuers ------------------------------
@@ -262,20 +334,22 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint64_t adesc0 = make_smem_desc(smem_u32(q_smem));
       const uint64_t bdesc00 = make_smem_desc(smem_u32(k_smem));
       const uint32_t d0 = tmem_base + b * F_ACC_COLS;
-      for (int item = blockIdx.x; item < nitems && !sh->abort_flag; item += gridDim.x, ++nblk) {
-        const int sp = item % nsplit;
-        const int t0 = sp * tps, t1 = (t0 + tps < ntiles) ? t0 + tps : ntiles;
-        const int nt = t1 > t0 ? t1 - t0 : 0;
+      for (;; ++nblk) {
         pc.start();
-        if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
+        if (!mbar_wait_sleeping(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
         pc.stop(0);
+        const int item = sh->item[nblk & 1u];
+        if (item < 0 || sh->abort_flag) break;
+        int t0, t1;
+        split_range(item % nsplit, nsplit, ntiles, t0, t1);
+        const int nt = t1 - t0;
         for (int j = b; j < nt; j += 2, ++use) {
           const uint32_t tuse = tbase + j;
           pc.start();
-          if (!mbar_wait_bounded(&sh->acc_empty[b], (use & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_sleeping(&sh->acc_empty[b], (use & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
           pc.stop(1);
           const uint32_t s = tuse % FNSTG;
-          if (!mbar_wait_bounded(&sh->k_full[s], (tuse / FNSTG) & 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_sleeping(&sh->k_full[s], (tuse / FNSTG) & 1u)) { sh->abort_flag = 1; break; }
           pc.stop(2);
           if (sh->abort_flag) break;
           tc_fence_after();
@@ -290,6 +364,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_commit(&sh->acc_full[b]);
           pc.stop(3);
         }
+        if (sh->abort_flag) break;
         tc_commit(&sh->q_empty);
         tbase += nt;
       }
@@ -299,30 +374,41 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else {
     // ------------------------------ epilogue: score, filter, append ------------------------------
     const int e = warp - 2;
-    const int strm = e >> 2;
-    const int lq = warp & 3;
+    const int half = e >> 2;   // column half of every tile this warp reduces
+    const int lq = warp & 3;   // TMEM lane quarter this warp may read
     const int row_in_tile = lq * 32 + lane;
-    // every warp works on every tile: stream 0 reduces its columns 0..31, stream 1 columns 32..63, so both
-    // accumulator sets are drained by all eight warps and the tensor cores never wait for half of them
-    const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + strm * F_HALF;
+    // every warp works on every tile, so both accumulator sets are drained by all eight warps and the tensor
+    // cores never wait for half of them
+    const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + half * F_QCOLS;
     const bool last_partial = (p.S % FBN) != 0;
+    const uint32_t list_bytes = static_cast<uint32_t>(p.caph) * 8u;
     uint32_t use0 = 0, use1 = 0, tbase = 0;
     ProfClock pc(p.profile != 0);
-    for (int item = blockIdx.x; item < nitems; item += gridDim.x) {
+    for (uint32_t nblk = 0;; ++nblk) {
+      pc.start();
+      if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
+      pc.stop(0);
+      const int item = sh->item[nblk & 1u];
+      if (item < 0 || sh->abort_flag) break;
       const int rb = blk_begin + item / nsplit, sp = item % nsplit;
-      const int t0 = sp * tps, t1 = (t0 + tps < ntiles) ? t0 + tps : ntiles;
-      const int nt = t1 > t0 ? t1 - t0 : 0;
+      int t0, t1;
+      split_range(sp, nsplit, ntiles, t0, t1);
+      const int nt = t1 - t0;
       const int row = rb * BM + row_in_tile;
       const bool active = row < p.T;
       const float tau = active ? p.tau_in[row] : INFINITY;
       const size_t lrow = static_cast<size_t>(row - p.row_begin);
-      const size_t seg = (lrow * nsplit + sp) * 2 + strm;  // this thread's list
-      uint2* const buf = p.cand + seg * p.caph;
-      uint2* wp = buf;
-      uint2* const wp_guard = buf + (p.caph - F_HALF);
-      bool overflowed = false;
+      const size_t seg = (lrow * nsplit + sp) * F_NQ + half;  // this thread's list
+      const uintptr_t buf = reinterpret_cast<uintptr_t>(p.cand + seg * p.caph);
+      const uint32_t lo0 = static_cast<uint32_t>(buf), hi = static_cast<uint32_t>(buf >> 32);
+      uint32_t lo = lo0;
+      // a list that wraps the low address word (the host places the lists so that none does) is not written at
+      // all: the row goes to the robust kernel and the status word says so
+      const bool wraps = lo0 + (list_bytes - 8u) < lo0;
+      bool overflowed = wraps;
+      const float tau_eff = wraps ? INFINITY : tau;
+      if (wraps) report_status(p.status, GW_ERR_INTERNAL);
       for (int jl = 0; jl < nt; ++jl) {
-        if (sh->abort_flag) break;
         const int j = t0 + jl;
         const uint32_t b = jl & 1;
         const uint32_t n = b ? use1 : use0;
@@ -333,17 +419,17 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!mbar_wait_bounded(&sh->w_full[ws], wn & 1u)) { sh->abort_flag = 1; break; }
         pc.stop(2);
         tc_fence_after();
-        // a list without room for a whole half tile is given up (the row is redone by the robust kernel): keep
-        // counting from the start of the list so that no store ever leaves it
-        if (wp > wp_guard) {
+        // a list without room for this warp's whole share of a tile is given up (the row is redone by the robust
+        // kernel): keep counting from the start of the list so that no store ever leaves it
+        if (lo - lo0 > list_bytes - F_QCOLS * 8u) {  // compared as offsets: a list may end exactly where the low word wraps
           overflowed = true;
-          wp = buf;
+          lo = lo0;
         }
         const float* wt = w_smem + ws * W_TILE_FLOATS;
         if (last_partial && j == ntiles - 1)
-          fast_reduce_tile<HI, true>(taddr_row + b * F_ACC_COLS, wt, strm * F_HALF, j * FBN, p.S, tau, wp);
+          fast_reduce_tile<HI, true>(taddr_row + b * F_ACC_COLS, wt, half * F_QCOLS, j * FBN, p.S, tau_eff, lo, hi);
         else
-          fast_reduce_tile<HI, false>(taddr_row + b * F_ACC_COLS, wt, strm * F_HALF, j * FBN, p.S, tau, wp);
+          fast_reduce_tile<HI, false>(taddr_row + b * F_ACC_COLS, wt, half * F_QCOLS, j * FBN, p.S, tau_eff, lo, hi);
         tc_fence_before();
         __syncwarp();
         pc.stop(3);
@@ -353,7 +439,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         if (b) ++use1; else ++use0;
       }
-      if (active) p.list_cnt[seg] = overflowed ? p.caph + 1 : static_cast<int>(wp - buf);
+      if (active) p.list_cnt[seg] = overflowed ? p.caph + 1 : static_cast<int>((lo - lo0) >> 3);
       tbase += nt;
       if (sh->abort_flag) break;
     }
@@ -368,7 +454,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------------------------
-// exact top-k of every row's two lists (one warp per row, many warps per SM to hide the list reads)
+// exact top-k of every row's lists (one warp per row, many warps per SM to hide the list reads)
 // ---------------------------------------------------------------------------------------------
 constexpr int FIN_WARPS = 8;
 
@@ -414,7 +500,7 @@ __global__ void __launch_bounds__(FIN_WARPS * 32) finalize_lists_kernel(const Id
   const int row = p.row_begin + blockIdx.x * FIN_WARPS + w;
   if (row >= p.row_end || row >= p.T) return;
   const size_t lrow = static_cast<size_t>(row - p.row_begin);
-  const int nseg = 2 * p.nsplit;
+  const int nseg = F_NQ * p.nsplit;
   const int* cnt = p.list_cnt + lrow * nseg;
   int n = 0;
   bool over = false;

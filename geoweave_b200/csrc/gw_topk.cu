@@ -778,6 +778,7 @@ extern "C" const char* gw_strerror(int code) {
     case GW_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
     case GW_ERR_NO_SM100: return "device is not compute capability 10.x";
     case GW_ERR_TOO_LARGE: return "problem exceeds the fixed capacity of a no-allocation entry point";
+    case GW_ERR_INTERNAL: return "a kernel found its own bookkeeping inconsistent and skipped the work";
     default: return "unknown geoweave_b200 status";
   }
 }

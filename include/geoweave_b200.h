@@ -37,6 +37,7 @@ typedef struct CUstream_st* gw_stream_t; /* a cudaStream_t */
 #define GW_ERR_TIMEOUT (-5)      /* device side: a bounded wait inside a kernel ran out (status word) */
 #define GW_ERR_NO_SM100 (-6)     /* the current device is not compute capability 10.x */
 #define GW_ERR_TOO_LARGE (-7)    /* the problem exceeds the fixed capacity of a no-allocation entry point */
+#define GW_ERR_INTERNAL (-8)     /* device side: a kernel found its own bookkeeping inconsistent and skipped the work (status word) */
 
 const char* gw_strerror(int code);
 int gw_last_cuda_error(void);   /* cudaError_t of the last GW_ERR_CUDA on this thread, else 0 */
