@@ -85,18 +85,22 @@ struct alignas(8) FastShared {
 // between polls the thread sleeps, so its polling does not take issue slots from the epilogue warps that share
 // its scheduler.  A wake-up that comes a few hundred cycles late is absorbed by the two accumulator sets and
 // the three key stages.  Bounded like every other wait.
-__device__ __forceinline__ bool mbar_wait_sleeping(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_sleeping(uint64_t* bar, uint32_t parity, uint32_t max_sleep_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
+  uint32_t ns = 64;
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
-      if (mbar_try_wait_hint(bar, parity, 4000u)) return true;  // suspended in hardware until the phase completes or ~4 us pass
-      __nanosleep(128);
+      __nanosleep(ns);
+      if (mbar_try_wait_hint(bar, parity, max_sleep_ns)) return true;
+      if (ns < max_sleep_ns) ns *= 2;  // back off: a poll costs eight issue slots of the scheduler it shares
     }
     if (global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
 }
+constexpr uint32_t kMmaSleepNs = 512;        // the tensor cores are one accumulator set ahead: a late wake-up costs nothing
+constexpr uint32_t kProducerSleepNs = 2048;  // the loads are three key stages ahead
 
 // packed fp32 pairs (sm_100 f32x2 pipe): d = a * b + c on both halves
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
@@ -276,7 +280,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (;; ++nblk) {
         if (item >= nitems) item = -1;
         pc.start();
-        if (!mbar_wait_sleeping(&sh->q_empty, (nblk & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+        if (!mbar_wait_sleeping(&sh->q_empty, (nblk & 1u) ^ 1u, kProducerSleepNs)) { sh->abort_flag = 1; break; }
         pc.stop(0);
         if (sh->abort_flag) break;
         sh->item[nblk & 1u] = item;  // made visible to the other roles by the arrival on q_full below
@@ -294,9 +298,9 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const uint32_t s = tuse % FNSTG, n = tuse / FNSTG;
           const uint32_t ws = tuse % WSLOTS, wn = tuse / WSLOTS;
           pc.start();
-          if (!mbar_wait_sleeping(&sh->k_empty[s], (n & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_sleeping(&sh->k_empty[s], (n & 1u) ^ 1u, kProducerSleepNs)) { sh->abort_flag = 1; break; }
           pc.stop(1);
-          if (!mbar_wait_sleeping(&sh->w_empty[ws], (wn & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_sleeping(&sh->w_empty[ws], (wn & 1u) ^ 1u, kProducerSleepNs)) { sh->abort_flag = 1; break; }
           pc.stop(2);
           if (sh->abort_flag) break;
           mbar_arrive_expect_tx(&sh->w_full[ws], W_TILE_BYTES);
@@ -336,7 +340,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t d0 = tmem_base + b * F_ACC_COLS;
       for (;; ++nblk) {
         pc.start();
-        if (!mbar_wait_sleeping(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
+        if (!mbar_wait_sleeping(&sh->q_full, nblk & 1u, kMmaSleepNs)) { sh->abort_flag = 1; break; }
         pc.stop(0);
         const int item = sh->item[nblk & 1u];
         if (item < 0 || sh->abort_flag) break;
@@ -346,10 +350,10 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int j = b; j < nt; j += 2, ++use) {
           const uint32_t tuse = tbase + j;
           pc.start();
-          if (!mbar_wait_sleeping(&sh->acc_empty[b], (use & 1u) ^ 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_sleeping(&sh->acc_empty[b], (use & 1u) ^ 1u, kMmaSleepNs)) { sh->abort_flag = 1; break; }
           pc.stop(1);
           const uint32_t s = tuse % FNSTG;
-          if (!mbar_wait_sleeping(&sh->k_full[s], (tuse / FNSTG) & 1u)) { sh->abort_flag = 1; break; }
+          if (!mbar_wait_sleeping(&sh->k_full[s], (tuse / FNSTG) & 1u, kMmaSleepNs)) { sh->abort_flag = 1; break; }
           pc.stop(2);
           if (sh->abort_flag) break;
           tc_fence_after();
@@ -388,8 +392,10 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       pc.start();
       if (!mbar_wait_bounded(&sh->q_full, nblk & 1u)) { sh->abort_flag = 1; break; }
       pc.stop(0);
-      const int item = sh->item[nblk & 1u];
-      if (item < 0 || sh->abort_flag) break;
+      // one value for the whole warp: through the shuffle the compiler also knows it, and keeps the tile loop and
+      // the tensor-memory addresses in the uniform datapath
+      const int item = __shfl_sync(0xffffffffu, sh->item[nblk & 1u], 0);
+      if (item < 0 || __shfl_sync(0xffffffffu, sh->abort_flag, 0)) break;
       const int rb = blk_begin + item / nsplit, sp = item % nsplit;
       int t0, t1;
       split_range(sp, nsplit, ntiles, t0, t1);
