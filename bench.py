@@ -52,6 +52,9 @@ def parse():
     ap.add_argument("--no-extra-legs", action="store_true",
                     help="skip the legs measured after the main region (attention in the HBM regime, the 256-view context, "
                          "operator inputs from the reference's projections)")
+    ap.add_argument("--attn-hbm", action="store_true",
+                    help="run only the attention kernel in the regime where HBM binds (8192 queries, k = 1024, positions uniformly "
+                         "random over 266496 keys: K + V = 1.09 GB) and print one JSON line; small enough for an ncu capture")
     ap.add_argument("--micro", action="store_true",
                     help="instead of the path, time the stand-alone operators (exact top-k of materialised scores, merge of "
                          "two lists, scalar attention kernels) and print one JSON line with their roofline fractions")
@@ -682,7 +685,26 @@ def run_micro(args):
     nbytes = 2 * N * width * 2 + N * 16  # every value read once and written once, plus the positions
     out.append({"op": "projection front-end epilogue (LayerNorm, rotary, layout), bf16", "shape": [N, width], "ms": ms, "bound": "hbm",
                 "achieved": nbytes / ms / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
-    # the whole layer as one call: fused projection (library GEMM) -> front-end -> indexer -> attention
+    # the projection itself: library GEMM alone, library GEMM + epilogue kernel, and the fused tensor-core kernel
+    import torch.nn.functional as Fnn
+    from geoweave_b200.front_end import project_fused
+    dimp = H * D
+    prm_p = FrontEndParams((torch.randn(width, dimp, device=dev) * dimp ** -0.5).bfloat16(), torch.zeros(width, device=dev).bfloat16(),
+                           H, HI, vec(), vec(), vec(), cos, sin)
+    xp = torch.randn(1, N, dimp, device=dev).bfloat16()
+    flops = 2.0 * N * width * dimp
+    try:
+        tc_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tc_peak = 1590.0
+    for name, fn in (("projection: library GEMM alone (cuBLAS, writes the raw product)", lambda: Fnn.linear(xp, prm_p.weight, prm_p.bias)),
+                     ("projection: library GEMM + epilogue kernel", lambda: project_epilogue(Fnn.linear(xp, prm_p.weight, prm_p.bias), fpos, prm_p)),
+                     ("projection: fused tcgen05 GEMM with LayerNorm / rotary / layout epilogue", lambda: project_fused(xp, fpos, prm_p))):
+        ms = timed(fn)
+        out.append({"op": name, "shape": [N, width, dimp], "ms": ms, "bound": "tensor", "achieved": flops / ms / 1e9, "peak": tc_peak,
+                    "unit": "TFLOP/s", "frac": flops / ms / 1e9 / tc_peak})
+    del xp
+    # the whole layer as one call: projection front-end -> indexer -> attention
     from geoweave_b200.layer import SparseGlobalAttentionLayer
     dim = H * D
     prm = FrontEndParams((torch.randn(width, dim, device=dev) * dim ** -0.5).bfloat16(), torch.zeros(width, device=dev).bfloat16(),
@@ -697,8 +719,43 @@ def run_micro(args):
     print(json.dumps({"micro": out}), flush=True)
 
 
+def run_attn_hbm(args):
+    """The sparse attention kernel alone on an index list that defeats the L2 (see --attn-hbm)."""
+    import geoweave_b200
+    from geoweave_b200 import _lib
+    from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
+
+    _lib.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    S_big, T_big, bf = 256 * 1041, 8192, torch.bfloat16
+    gg = torch.Generator(device=dev).manual_seed(99)
+    kb = torch.randn(1, S_big, H, D, device=dev, dtype=bf, generator=gg)
+    vb = torch.randn(1, S_big, H, D, device=dev, dtype=bf, generator=gg)
+    qb = torch.randn(1, T_big, H, D, device=dev, dtype=bf, generator=gg)
+    pb = torch.randint(0, S_big, (1, T_big, TOPK), device=dev, dtype=torch.int32, generator=gg)
+    fn = lambda: sparse_index_flash_attn_inference_func(qb, kb, vb, pb, None, False, D ** -0.5, False)
+    for _ in range(max(1, args.warmup)):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(max(1, args.steps)):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    geoweave_b200.check_status()
+    ms = a.elapsed_time(b) / max(1, args.steps)
+    nbytes = T_big * (TOPK * 2 * H * D * 2 + TOPK * 4 + 2 * H * D * 2)
+    print(json.dumps({"leg": "attention, HBM regime", "queries": T_big, "keys": S_big, "topk": TOPK, "ms_per_launch": ms,
+                      "bytes_per_launch": nbytes, "achieved_gbs": nbytes / ms / 1e6}), flush=True)
+
+
 def main():
     args = parse()
+    if args.attn_hbm:
+        run_attn_hbm(args)
+        return
     if args.micro:
         run_micro(args)
         return

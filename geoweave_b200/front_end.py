@@ -120,6 +120,54 @@ def project_epilogue(fused: torch.Tensor, pos: Optional[torch.Tensor], prm: Fron
     return tuple(out)
 
 
+def project_fused(x: torch.Tensor, pos: Optional[torch.Tensor], prm: FrontEndParams):
+    """Layer input ``x [B,N,dim]`` (bf16 / fp16, ``dim`` a multiple of 64) -> the six operator inputs in ONE kernel: the
+    projection GEMM on the tcgen05 tensor cores with bias, LayerNorm, rotary embedding and the token-major stores in
+    its epilogue.  The raw product ``[q | k | v | idx_q | idx_k | idx_w]`` never reaches memory."""
+    lib = _lib.load()
+    dev = _lib.require_cuda(x)
+    if x.dim() != 3:
+        raise ValueError(f"x must be [B,N,dim], got shape={tuple(x.shape)}")
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("the fused projection takes bfloat16 or float16 tokens (fp32: project_epilogue after a library GEMM)")
+    B, N, dim = x.shape
+    H, Hi = prm.heads, prm.idx_heads
+    width = 3 * H * HEAD_DIM + 2 * Hi * HEAD_DIM + Hi
+    if tuple(prm.weight.shape) != (width, dim):
+        raise ValueError(f"weight must be [{width}, {dim}], got {tuple(prm.weight.shape)}")
+    if dim % 64 != 0:
+        raise _lib.GeoWeaveError(-2, "the fused projection needs a model width that is a multiple of 64")
+    x = x.contiguous()
+    weight = prm.weight.to(dev, x.dtype).contiguous()
+    bias = None if prm.bias is None else prm.bias.to(dev, x.dtype).contiguous()
+    if pos is not None:
+        if prm.cos is None:
+            raise ValueError("positions given but the parameters hold no rotary tables")
+        if tuple(pos.shape) != (B, N, 2):
+            raise ValueError(f"pos must be [B,N,2], got shape={tuple(pos.shape)}")
+        pos = pos.to(device=dev, dtype=torch.int64).contiguous()
+    out = [torch.empty((B, N, H, HEAD_DIM), device=dev, dtype=x.dtype) for _ in range(3)]
+    out += [torch.empty((B, N, Hi, HEAD_DIM), device=dev, dtype=x.dtype) for _ in range(2)]
+    out.append(torch.empty((B, N, Hi), device=dev, dtype=x.dtype))
+    norms = [None if n is None else (n[0].to(dev, torch.float32).contiguous(), n[1].to(dev, torch.float32).contiguous(), float(n[2]))
+             for n in (prm.q_norm, prm.k_norm, prm.idx_k_norm)]
+    qn, kn, ikn = [(None, None, 0.0) if n is None else (n[0].data_ptr(), n[1].data_ptr(), n[2]) for n in norms]
+    cos = prm.cos.to(dev, torch.float32).contiguous() if pos is not None else None
+    sin = prm.sin.to(dev, torch.float32).contiguous() if pos is not None else None
+    with torch.cuda.device(dev):
+        rc = lib.gw_project_fused(x.data_ptr(), weight.data_ptr(), _lib.ptr(bias), _lib.dtype_code(x), B * N, dim, H, HEAD_DIM, Hi,
+                                  HEAD_DIM, _lib.ptr(pos), _lib.ptr(cos), _lib.ptr(sin), 0 if cos is None else cos.shape[0],
+                                  qn[0], qn[1], qn[2], kn[0], kn[1], kn[2], ikn[0], ikn[1], ikn[2], *[t.data_ptr() for t in out],
+                                  _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "gw_project_fused")
+    del norms, cos, sin, weight, bias
+    return tuple(out)
+
+
 def project_qkv_and_indexer(x: torch.Tensor, pos: Optional[torch.Tensor], prm: FrontEndParams):
-    """Layer input ``x [B,N,dim]`` -> the six operator inputs: one library GEMM, one kernel."""
+    """Layer input ``x [B,N,dim]`` -> the six operator inputs.  16-bit tokens of a width that is a multiple of 64 go
+    through the fused tensor-core kernel (``project_fused``); fp32 tokens, whose products the 16-bit tensor-core path
+    would change, through a library GEMM followed by the epilogue kernel."""
+    if x.dtype in (torch.bfloat16, torch.float16) and x.shape[-1] % 64 == 0:
+        return project_fused(x, pos, prm)
     return project_epilogue(F.linear(x, prm.weight, prm.bias), pos, prm)

@@ -189,6 +189,23 @@ int gw_project_epilogue(const void* fused, int dtype, int64_t tokens, int64_t ld
                         float idx_k_norm_eps, void* q, void* k, void* v, void* q_idx, void* k_idx, void* w,
                         int* status_dev, gw_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * The projection itself, fused with gw_project_epilogue's work: [q | k | v | idx_q | idx_k | idx_w] = x . weight^T + bias
+ * on the tcgen05 tensor cores (fp32 accumulation), then per head LayerNorm / rotary embedding as in
+ * gw_project_epilogue on the fp32 accumulators, one rounding, token-major stores.  The raw product never reaches memory.
+ * x [tokens, dim], weight [3*H*D + 2*Hi*Di + Hi, dim] (rows ordered qkv ([3][H][D]), idx_q, idx_k, idx_w), bias
+ * [same rows] or null, all of `dtype` (GW_BF16 or GW_F16), contiguous.  Everything else as gw_project_epilogue.
+ * Requirements: D = Di = 64, dim a multiple of 64, Hi <= 32, 16-byte aligned pointers.
+ * Replaces: easyvolcap/official_vggt/layers/dsa_attention.py:545-627 (_project_qkv_and_indexer_fused: the F.linear
+ *           over the concatenated weights and the split that follows), together with everything gw_project_epilogue replaces.
+ * ---------------------------------------------------------------------------------------------- */
+int gw_project_fused(const void* x, const void* weight, const void* bias, int dtype, int64_t tokens, int dim, int H, int D,
+                     int Hi, int Di, const int64_t* pos, const float* cos_tab, const float* sin_tab, int table_rows,
+                     const float* q_norm_w, const float* q_norm_b, float q_norm_eps, const float* k_norm_w,
+                     const float* k_norm_b, float k_norm_eps, const float* idx_k_norm_w, const float* idx_k_norm_b,
+                     float idx_k_norm_eps, void* q, void* k, void* v, void* q_idx, void* k_idx, void* w, int* status_dev,
+                     gw_stream_t stream);
+
 /* Diagnostics: the gather of gw_sparse_attn_fwd without its arithmetic -- for every query the K row and the V row
  * (row_bytes <= 2048, a multiple of 16; rows k_row_stride_bytes / v_row_stride_bytes apart) of each valid entry of
  * kv_pos int32 [T,K] is bulk-copied into shared memory and dropped.  Timed by the caller, it gives the rate this

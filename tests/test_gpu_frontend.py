@@ -72,6 +72,66 @@ def test_linear_plus_epilogue_from_the_layer_input(fe_golden, name, dtype):
         assert bool((err <= 2 * tolerance(ref, dtype) + (1e-4 if dtype == torch.float32 else 0)).all()), (name, nm, float(err.max()))
 
 
+@pytest.mark.parametrize("name", ["fe_bf16", "fe_pi3_bf16"])
+def test_fused_projection_on_the_reference_fixtures(fe_golden, name):
+    """x -> the six operator inputs in ONE kernel (tensor-core GEMM with the LayerNorm / rotary / layout epilogue) against
+    what the reference's own modules produced from the same x and weights."""
+    import geoweave_b200
+    from geoweave_b200.front_end import project_fused
+
+    c = fe_golden[name]
+    dtype = torch.bfloat16
+    prm = params_of(c, dev(), dtype)
+    outs = project_fused(T(c["x"], dtype).to(dev()), T(c["pos"]).to(dev()), prm)
+    geoweave_b200.check_status()
+    for nm, o in zip(NAMES, outs):
+        ref = T(c[nm])
+        assert o.dtype == dtype and tuple(o.shape) == tuple(ref.shape) and o.is_contiguous(), nm
+        err = (o.float().cpu() - ref).abs()
+        # the reference rounds the product to bf16 before LayerNorm and after every later step, this kernel once at the end
+        assert bool((err <= 2 * tolerance(ref, dtype)).all()), (name, nm, float(err.max()))
+
+
+@pytest.mark.parametrize("dtype,heads,idx_heads,tokens,dim,bias,norms,rope", [
+    (torch.bfloat16, 16, 4, 4164, 1024, True, True, True),    # the models' shape: 4 views
+    (torch.bfloat16, 16, 4, 1000, 1024, False, False, True),  # ragged last row tile, no bias, no LayerNorm
+    (torch.float16, 8, 3, 777, 256, True, True, False),       # fp16, odd number of indexer heads, no rotary embedding
+    (torch.bfloat16, 3, 1, 130, 64, True, True, True),        # head slots of different kinds inside one column tile
+])
+def test_fused_projection_against_the_oracle(dtype, heads, idx_heads, tokens, dim, bias, norms, rope):
+    """The fused kernel against the oracle's front end applied to the exact (fp32) product of the same 16-bit x and W."""
+    import geoweave_b200
+    from geoweave_b200.front_end import FrontEndParams, project_fused, rope_tables
+
+    g = torch.Generator().manual_seed(tokens + heads)
+    width = 3 * heads * 64 + 2 * idx_heads * 64 + idx_heads
+    x = torch.randn(1, tokens, dim, generator=g).to(dtype)
+    wt = (torch.randn(width, dim, generator=g) * dim ** -0.5).to(dtype)
+    bs = (torch.randn(width, generator=g) * 0.2).to(dtype) if bias else None
+    pos = torch.randint(0, 38, (1, tokens, 2), generator=g)
+    cos, sin = rope_tables(38, "cpu", dtype)
+    vec = lambda: (torch.randn(64, generator=g) * 0.3 + 1.0, torch.randn(64, generator=g) * 0.2, 1e-5)
+    qn, kn, ikn = (vec(), vec(), vec()) if norms else (None, None, None)
+    prm = FrontEndParams(wt.to(dev()), None if bs is None else bs.to(dev()), heads, idx_heads, qn, kn, ikn, cos, sin)
+    outs = project_fused(x.to(dev()), pos.to(dev()) if rope else None, prm)
+    geoweave_b200.check_status()
+    fused = x.double()[0] @ wt.double().T
+    if bs is not None:
+        fused = fused + bs.double()
+    fused = fused.float().unsqueeze(0)
+    if rope:
+        refs = orc.project_front_end(fused, pos, cos, sin, heads, 64, idx_heads, 64, qn, kn, ikn)
+    else:
+        refs = orc.project_front_end(fused, torch.zeros_like(pos), torch.ones(1, 32), torch.zeros(1, 32), heads, 64, idx_heads, 64,
+                                     qn, kn, ikn)
+    for nm, o, ref in zip(NAMES, outs, refs):
+        assert o.dtype == dtype and tuple(o.shape) == tuple(ref.shape), nm
+        err = (o.float().cpu() - ref).abs()
+        ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+        # one rounding to the 16-bit type; the fp32 accumulation order of the tensor cores is below that
+        assert bool((err <= 1.01 * ulp * ref.abs() + 2e-3).all()), (nm, float(err.max()))
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("heads,views", [(16, 8), (8, 3)])
 def test_production_width_against_the_oracle(dtype, heads, views):
