@@ -542,9 +542,12 @@ def run_ours(args):
                 "clocks": clk}
         if hbm_leg:
             gbs = hbm_leg["bytes"] / (hbm_leg["ms"] * 1e-3) / 1e9
+            hbm_traffic = recorded_dram_traffic("sparse_attn_mma_kernel", "attn_hbm", hbm_leg["queries"])
             line["roofline_hbm"] = {
                 "kernel": "sparse_attn_mma_kernel", "bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
-                "frac": gbs / hbm_peak, "traffic": None, "peak_source": peak_src, "ms_per_launch": hbm_leg["ms"],
+                "frac": gbs / hbm_peak, "traffic": hbm_traffic,
+                "dram_frac": (hbm_traffic / (hbm_leg["ms"] * 1e-3) / 1e9 / hbm_peak) if hbm_traffic else None,
+                "peak_source": peak_src, "ms_per_launch": hbm_leg["ms"],
                 "bytes_per_launch": hbm_leg["bytes"],
                 "gather_ceiling": {"achieved": hbm_leg["bytes"] / (hbm_leg["gather_ms"] * 1e-3) / 1e9, "unit": "GB/s",
                                    "ms": hbm_leg["gather_ms"], "frac_of_ceiling": hbm_leg["gather_ms"] / hbm_leg["ms"]},
@@ -588,10 +591,10 @@ def recorded_dram_traffic(kernel, workload, rows):
     bench_traffic.json -- only if that capture was made of the kernel source as it is now (digest match);
     scaled by the rows of this launch for a sharded run.  None otherwise."""
     try:
-        rec = json.load(open(os.path.join(ROOT, "bench_traffic.json")))[kernel]
+        rec = json.load(open(os.path.join(ROOT, "bench_traffic.json")))[f"{kernel}/{workload}"]
     except Exception:
         return None
-    if rec.get("workload") != workload or rec.get("source_sha256") != kernel_source_digest():
+    if rec.get("source_sha256") != kernel_source_digest():
         return None
     return float(rec["dram_bytes_per_launch"]) * rows / float(rec["rows"])
 
