@@ -674,6 +674,17 @@ def run_micro(args):
         ms = timed(lambda: sparse_attention_forward(q, kk, vv, pos, None, with_sum, with_sum, "bthd"), reps=3)
         out.append({"op": name, "shape": [T, S, TOPK], "ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak,
                     "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
+    # the backward of the same call (dQ, dK, dV; the index lists sorted by key inside the timed call)
+    from geoweave_b200.custom_flash_attn.sparse_index_flash_attn import sparse_attention_backward
+    o_f, _, lse_f = sparse_attention_forward(q, kk, vv, pos, None, False, True, "bthd")
+    d_o = torch.randn_like(o_f)
+    ms = timed(lambda: sparse_attention_backward(q, kk, vv, pos, o_f, lse_f, d_o, None, None), reps=3)
+    # per (query, key) pair: the K and V rows, then from the key's side the q and dO rows; P and dP written and read once
+    nbytes_bwd = T * TOPK * (4 * H * D * 2 + 4 * H * 4) + T * TOPK * 12
+    out.append({"op": "sparse attention backward (query kernel + key kernel + sort of the lists), bf16", "shape": [T, S, TOPK],
+                "ms": ms, "bound": "hbm", "achieved": nbytes_bwd / ms / 1e6, "peak": hbm_peak, "unit": "GB/s",
+                "frac": nbytes_bwd / ms / 1e6 / hbm_peak})
+    del o_f, lse_f, d_o
     # projection front-end on the benchmark's shape: 33 312 tokens, 16 heads + 4 indexer heads (VGGT grid positions)
     from geoweave_b200.front_end import FrontEndParams, project_epilogue, rope_tables
     del q, kk, vv, pos

@@ -1,4 +1,4 @@
-"""Sparse-index flash attention, forward only -- same call signatures as the reference module
+"""Sparse-index flash attention, forward and backward -- same call signatures as the reference module
 ``easyvolcap/utils/custom_flash_attn/sparse_index_flash_attn.py`` (entry points at :3139, :3168, :3286, :3370).
 
 Every function runs the hand-written sm_100a kernel behind ``gw_sparse_attn_fwd``; there is no Triton and
@@ -22,6 +22,7 @@ __all__ = [
     "dense_index_flash_attn_func",
     "sparse_index_flash_attn_value_gate_bhtd_func",
     "sparse_attention_forward",
+    "sparse_attention_backward",
 ]
 
 
@@ -115,18 +116,76 @@ def sparse_index_flash_attn_inference_bhtd_func(q, k, v, kv_positions, bias: Opt
     return o, attn_sum
 
 
-def _no_grad_inputs(*tensors):
-    if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
-        raise NotImplementedError(
-            "geoweave_b200 implements the forward pass only; call under torch.no_grad()/inference_mode() "
-            "or detach q/k/v (the backward kernels of the reference are outside this library's scope)")
+def sparse_attention_backward(q, k, v, kv_positions, o, lse, d_out, d_attn_sum, softmax_scale):
+    """Gradients of the forward for ``[B,T,H,D]`` / ``[B,S,H,D]`` tensors: ``(dq, dk, dv)`` of the inputs' dtype.
+
+    ``d_attn_sum`` (fp32 ``[B,T,K]`` or None) is the gradient arriving through the forward's second result.  The sums
+    over the queries that selected a key run in a fixed order (the index lists are stably sorted by key first, here
+    with ``torch.sort``), so the result is reproducible; there are no floating-point atomics in the kernels."""
+    dev = _lib.require_cuda(q, k, v, kv_positions, o, d_out)
+    B, T, H, D = q.shape
+    S = k.shape[1]
+    K = kv_positions.shape[-1]
+    if D != 64 or H > 32:
+        raise NotImplementedError("the backward kernels are built for head_dim 64 and at most 32 heads")
+    q, k, v, o, d_out = [x.contiguous() for x in (q, k, v, o, d_out.to(q.dtype))]
+    kv_positions = kv_positions.contiguous()
+    lse = lse.contiguous()
+    if d_attn_sum is not None:
+        d_attn_sum = d_attn_sum.to(torch.float32).contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if T == 0 or K == 0:
+        return dq.zero_(), dk.zero_(), dv.zero_()
+    # (query, slot) pairs grouped by key, in a fixed order: padding entries sort behind the last key
+    flat = kv_positions.view(B, T * K).to(torch.int64)
+    flat = torch.where((flat < 0) | (flat >= S), torch.full_like(flat, S), flat)
+    keys_sorted, order = torch.sort(flat, dim=1, stable=True)
+    bounds = torch.arange(S + 1, device=dev, dtype=torch.int64).unsqueeze(0).expand(B, S + 1).contiguous()
+    start = torch.searchsorted(keys_sorted, bounds).to(torch.int32).contiguous()
+    order = order.to(torch.int32).contiguous()
+    lib = _lib.load()
+    ws = torch.empty(int(lib.gw_sparse_attn_bwd_workspace_bytes(B, T, H, K)), dtype=torch.uint8, device=dev)
+    scale = float(softmax_scale) if softmax_scale else 1.0 / math.sqrt(D)
+    with torch.cuda.device(dev):
+        rc = lib.gw_sparse_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), kv_positions.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                    d_out.data_ptr(), _lib.ptr(d_attn_sum), order.data_ptr(), start.data_ptr(), _lib.dtype_code(q),
+                                    B, T, S, H, D, K, scale, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel(),
+                                    _lib.stream_ptr(dev))
+    _lib.check(rc, "gw_sparse_attn_bwd")
+    return dq, dk, dv
+
+
+class _SparseIndexFlashAttn(torch.autograd.Function):
+    """The reference's ``SparseIndexFlashAttnFunc`` / ``SparseIndexFlashAttnBhtdFunc`` (:3196-3370): forward returns
+    ``(o, attn_sum)``, backward returns the gradients of q, k and v (both results may carry a gradient)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, kv_positions, softmax_scale, layout):
+        o, attn_sum, lse = sparse_attention_forward(q, k, v, kv_positions, softmax_scale, True, True, layout)
+        ctx.save_for_backward(q, k, v, kv_positions, o, lse)
+        ctx.softmax_scale = softmax_scale
+        ctx.layout = layout
+        return o, attn_sum
+
+    @staticmethod
+    def backward(ctx, d_o, d_attn_sum):
+        q, k, v, kv_positions, o, lse = ctx.saved_tensors
+        to_bthd = (lambda x: x.transpose(1, 2)) if ctx.layout == "bhtd" else (lambda x: x)
+        dq, dk, dv = sparse_attention_backward(to_bthd(q), to_bthd(k), to_bthd(v), kv_positions, to_bthd(o), lse, to_bthd(d_o),
+                                               d_attn_sum, ctx.softmax_scale)
+        return to_bthd(dq), to_bthd(dk), to_bthd(dv), None, None, None
+
+
+def _wants_grad(*tensors):
+    return torch.is_grad_enabled() and any(t.requires_grad for t in tensors)
 
 
 def sparse_index_flash_attn_func(q, k, v, kv_positions, bias=None, causal=False, softmax_scale=None):
-    """Forward of the reference's autograd entry (``SparseIndexFlashAttnFunc.apply``): returns ``(o, attn_sum)``
-    with ``attn_sum`` fp32 ``[B,T,K]``.  Inputs that require grad are refused."""
+    """The reference's autograd entry (``SparseIndexFlashAttnFunc.apply``): returns ``(o, attn_sum)`` with ``attn_sum``
+    fp32 ``[B,T,K]``; differentiable in q, k and v."""
     _reject(bias, causal)
-    _no_grad_inputs(q, k, v)
+    if _wants_grad(q, k, v):
+        return _SparseIndexFlashAttn.apply(q, k, v, kv_positions, softmax_scale, "bthd")
     with torch.no_grad():
         o, attn_sum, _ = sparse_attention_forward(q, k, v, kv_positions, softmax_scale, True, False, "bthd")
     return o, attn_sum
@@ -134,7 +193,8 @@ def sparse_index_flash_attn_func(q, k, v, kv_positions, bias=None, causal=False,
 
 def sparse_index_flash_attn_bhtd_func(q, k, v, kv_positions, bias=None, causal=False, softmax_scale=None):
     _reject(bias, causal)
-    _no_grad_inputs(q, k, v)
+    if _wants_grad(q, k, v):
+        return _SparseIndexFlashAttn.apply(q, k, v, kv_positions, softmax_scale, "bhtd")
     with torch.no_grad():
         o, attn_sum, _ = sparse_attention_forward(q, k, v, kv_positions, softmax_scale, True, False, "bhtd")
     return o, attn_sum

@@ -57,7 +57,7 @@ def test_bhtd_layout_and_strided_views(golden, name):
         assert torch.equal(o_v, o_ref)
 
 
-def test_autograd_entry_returns_attn_sum_and_refuses_grad(golden):
+def test_autograd_entry_returns_attn_sum_and_refuses_bias(golden):
     from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_func
 
     c = golden["attn_h4"]
@@ -65,8 +65,8 @@ def test_autograd_entry_returns_attn_sum_and_refuses_grad(golden):
     o, attn_sum = sparse_index_flash_attn_func(q, k, v, t(c["idx"]), None, False, float(c["scale"]))
     assert attn_sum.dtype == torch.float32 and attn_sum.shape == c["attn_sum"].shape
     torch.testing.assert_close(attn_sum.sum(-1).cpu(), torch.full(attn_sum.shape[:2], float(q.shape[2])), rtol=0, atol=2e-2)
-    with pytest.raises(NotImplementedError):
-        sparse_index_flash_attn_func(q.requires_grad_(), k, v, t(c["idx"]))
+    o_g, _ = sparse_index_flash_attn_func(q.clone().requires_grad_(), k, v, t(c["idx"]), None, False, float(c["scale"]))
+    assert o_g.requires_grad and torch.equal(o_g.detach(), o)  # the differentiable path runs the same forward kernel
     with pytest.raises(NotImplementedError):
         sparse_index_flash_attn_func(q.detach(), k, v, t(c["idx"]), torch.zeros(1, device=dev()))
 
