@@ -9,6 +9,9 @@
 //   ds = p (dp' - delta') scale
 //   dQ[t,h] = sum_j ds K[pos[t,j],h]        dK[s,h] = sum_{(t,j): pos[t,j]=s} ds q[t,h]       dV[s,h] = sum_{...} p dO[t,h]
 //
+// 16-bit inputs with 8 or 16 heads and no gradient through attn_sum take the tensor-core kernels of gw_attn_bwd_mma.cuh;
+// everything else (fp32, other head counts, a gradient through attn_sum) takes the two kernels of this file.
+//
 // Two kernels.  The query kernel (one CTA per query, one warp per head at a time, one lane per selected key)
 // gathers the key's K and V slices, forms p and dp', writes both to a scratch of the shape [B,T,H,K], and gets dQ
 // in the same pass from two running sums, A = sum p dp' K and Bk = sum p K, since dQ = scale (A - delta' Bk) needs
@@ -19,6 +22,7 @@
 // (easyvolcap/utils/custom_flash_attn/sparse_index_flash_attn.py:535-1186, 2442-2846) or, opt-in, with a sort-based
 // grouped kernel (csrc/sparse_bwd_grouped_kernel.cu:78-603).
 #include "gw_common.cuh"
+#include "gw_attn_bwd_mma.cuh"
 
 namespace gw {
 namespace {
@@ -235,7 +239,7 @@ extern "C" size_t gw_sparse_attn_bwd_workspace_bytes(int B, int T, int H, int K)
 extern "C" int gw_sparse_attn_bwd(const void* q, const void* k, const void* v, const int32_t* kv_pos, const void* out, const float* lse,
                                   const void* d_out, const float* d_attn_sum, const int32_t* key_order, const int32_t* key_start,
                                   int dtype, int B, int T, int S, int H, int D, int K, float scale, void* dq, void* dk, void* dv,
-                                  void* workspace, size_t workspace_bytes, gw_stream_t stream) {
+                                  void* workspace, size_t workspace_bytes, int* status_dev, gw_stream_t stream) {
   if (!q || !k || !v || !kv_pos || !out || !lse || !d_out || !key_order || !key_start || !dq || !dk || !dv)
     return GW_ERR_INVALID_ARG;
   if (B <= 0 || T < 0 || S <= 0 || H <= 0 || K <= 0 || B > 65535) return GW_ERR_INVALID_ARG;
@@ -256,6 +260,14 @@ extern "C" int gw_sparse_attn_bwd(const void* q, const void* k, const void* v, c
   p.delta = reinterpret_cast<float*>(ws + 2 * round_up(n * K * sizeof(float), 256));
   p.dq = dq; p.dk = dk; p.dv = dv; p.B = B; p.T = T; p.S = S; p.H = H; p.K = K; p.scale = scale;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype != GW_F32 && d_attn_sum == nullptr && (H == 8 || H == 16) && status_dev != nullptr) {
+    BwdMmaParams m;
+    m.q = q; m.k = k; m.v = v; m.o = out; m.d_out = d_out; m.pos = kv_pos; m.lse = lse;
+    m.key_order = key_order; m.key_start = key_start; m.pds = reinterpret_cast<uint32_t*>(ws);
+    m.dq = dq; m.dk = dk; m.dv = dv; m.status = status_dev; m.B = B; m.T = T; m.S = S; m.H = H; m.K = K; m.scale = scale;
+    if (dtype == GW_BF16) return H == 16 ? launch_bwd_mma<__nv_bfloat16, 2>(m, st) : launch_bwd_mma<__nv_bfloat16, 1>(m, st);
+    return H == 16 ? launch_bwd_mma<__half, 2>(m, st) : launch_bwd_mma<__half, 1>(m, st);
+  }
   switch (dtype) {
     case GW_F32: return launch_bwd<float>(p, st);
     case GW_BF16: return launch_bwd<__nv_bfloat16>(p, st);

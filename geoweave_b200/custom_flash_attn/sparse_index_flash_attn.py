@@ -150,8 +150,10 @@ def sparse_attention_backward(q, k, v, kv_positions, o, lse, d_out, d_attn_sum, 
         rc = lib.gw_sparse_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), kv_positions.data_ptr(), o.data_ptr(), lse.data_ptr(),
                                     d_out.data_ptr(), _lib.ptr(d_attn_sum), order.data_ptr(), start.data_ptr(), _lib.dtype_code(q),
                                     B, T, S, H, D, K, scale, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr(), ws.numel(),
-                                    _lib.stream_ptr(dev))
+                                    _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "gw_sparse_attn_bwd")
+    if _lib.debug_enabled():
+        _lib.check_status(dev)
     return dq, dk, dv
 
 
@@ -163,6 +165,7 @@ class _SparseIndexFlashAttn(torch.autograd.Function):
     def forward(ctx, q, k, v, kv_positions, softmax_scale, layout):
         o, attn_sum, lse = sparse_attention_forward(q, k, v, kv_positions, softmax_scale, True, True, layout)
         ctx.save_for_backward(q, k, v, kv_positions, o, lse)
+        ctx.set_materialize_grads(False)  # a result the loss does not use arrives as None, not as a tensor of zeros
         ctx.softmax_scale = softmax_scale
         ctx.layout = layout
         return o, attn_sum
@@ -171,6 +174,8 @@ class _SparseIndexFlashAttn(torch.autograd.Function):
     def backward(ctx, d_o, d_attn_sum):
         q, k, v, kv_positions, o, lse = ctx.saved_tensors
         to_bthd = (lambda x: x.transpose(1, 2)) if ctx.layout == "bhtd" else (lambda x: x)
+        if d_o is None:
+            d_o = torch.zeros_like(o)
         dq, dk, dv = sparse_attention_backward(to_bthd(q), to_bthd(k), to_bthd(v), kv_positions, to_bthd(o), lse, to_bthd(d_o),
                                                d_attn_sum, ctx.softmax_scale)
         return to_bthd(dq), to_bthd(dk), to_bthd(dv), None, None, None

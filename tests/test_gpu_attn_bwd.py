@@ -44,7 +44,10 @@ def make(B, T, S, H, K, dtype, seed, pad=True):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 1e-2), (torch.float16, 1e-2)])
-@pytest.mark.parametrize("B,T,S,H,K,with_sum", [(1, 150, 400, 16, 96, False), (2, 90, 250, 4, 33, True), (1, 64, 64, 2, 64, True)])
+# 16-bit, 8 or 16 heads, no gradient through attn_sum: the tensor-core kernels; every other row: the plain kernels
+@pytest.mark.parametrize("B,T,S,H,K,with_sum", [(1, 150, 400, 16, 96, False), (2, 90, 250, 8, 33, False), (1, 300, 100, 16, 50, False),
+                                                (1, 40, 3000, 16, 7, False), (1, 150, 400, 16, 96, True), (2, 90, 250, 4, 33, True),
+                                                (1, 64, 64, 2, 64, True)])
 def test_backward_matches_autograd_of_the_plain_formulation(dtype, tol, B, T, S, H, K, with_sum):
     from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_func
 
@@ -102,3 +105,18 @@ def test_forward_only_calls_still_take_no_graph_and_bad_shapes_are_refused():
     with pytest.raises(NotImplementedError):
         sparse_attention_backward(q32, q32, q32, torch.zeros(1, 4, 2, dtype=torch.int32, device=dev()), q32,
                                   torch.zeros(1, 2, 4, device=dev()), q32, None, None)
+
+
+def test_gradient_through_attn_sum_alone():
+    from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_func
+
+    q, k, v, pos, _, d_a = make(1, 70, 120, 8, 24, torch.bfloat16, seed=9)
+    qd, kd, vd = [x.to(dev()).requires_grad_() for x in (q, k, v)]
+    _, attn_sum = sparse_index_flash_attn_func(qd, kd, vd, pos.to(dev()), None, False, 0.125)
+    (attn_sum * d_a.to(dev())).sum().backward()
+    qr, kr, vr = [x.float().to(dev()).requires_grad_() for x in (q, k, v)]
+    _, a_ref = reference_forward(qr, kr, vr, pos.to(dev()).long(), 0.125)
+    (a_ref * d_a.to(dev())).sum().backward()
+    for got, ref in ((qd.grad, qr.grad), (kd.grad, kr.grad)):
+        assert (got.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+    assert vd.grad is None or vd.grad.abs().max().item() == 0.0  # attn_sum does not depend on v
