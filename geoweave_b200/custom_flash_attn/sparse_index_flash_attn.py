@@ -13,6 +13,7 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
+from .._lists import group_by_key
 
 __all__ = [
     "sparse_index_flash_attn_inference_func",
@@ -136,13 +137,7 @@ def sparse_attention_backward(q, k, v, kv_positions, o, lse, d_out, d_attn_sum, 
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     if T == 0 or K == 0:
         return dq.zero_(), dk.zero_(), dv.zero_()
-    # (query, slot) pairs grouped by key, in a fixed order: padding entries sort behind the last key
-    flat = kv_positions.view(B, T * K).to(torch.int64)
-    flat = torch.where((flat < 0) | (flat >= S), torch.full_like(flat, S), flat)
-    keys_sorted, order = torch.sort(flat, dim=1, stable=True)
-    bounds = torch.arange(S + 1, device=dev, dtype=torch.int64).unsqueeze(0).expand(B, S + 1).contiguous()
-    start = torch.searchsorted(keys_sorted, bounds).to(torch.int32).contiguous()
-    order = order.to(torch.int32).contiguous()
+    order, start = group_by_key(kv_positions, S)  # (query, slot) pairs grouped by key, in a fixed order
     lib = _lib.load()
     ws = torch.empty(int(lib.gw_sparse_attn_bwd_workspace_bytes(B, T, H, K)), dtype=torch.uint8, device=dev)
     scale = float(softmax_scale) if softmax_scale else 1.0 / math.sqrt(D)

@@ -18,9 +18,10 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
+from .._lists import group_by_key
 
 __all__ = ["sparse_topk_indexer_func", "sparse_topk_indexer_inference_func", "indexer_scores", "indexer_workspace_bytes",
-           "clear_runtime_cache"]
+           "indexer_topk_backward", "clear_runtime_cache"]
 
 clear_runtime_cache = _lib.clear_runtime_cache
 
@@ -153,13 +154,76 @@ def _reject_mask(mask, view_bias_data):
         raise NotImplementedError("soft view bias is a training-time option and is not implemented")
 
 
+def indexer_topk_backward(q, k, w, topk_indices, grad_scores, softmax_scale: Optional[float]):
+    """Gradients of the selected scores ``score[t,j] = sum_h w[idx[t,j],h] * relu(scale * q[t,h].k[idx[t,j],h])`` with
+    respect to q, k and w, given ``grad_scores`` ``[B,T,k]`` -- the reference's ``_backward_selected_topk_qkw`` (:757-895).
+    Entries of ``topk_indices`` outside ``[0, S)`` carry no gradient.  The sums over the queries that selected a key run
+    in a fixed order (no floating-point atomics), so the result is reproducible.  16-bit operands, head_dim 64, at most
+    four heads."""
+    dev = _lib.require_cuda(q, k, w, topk_indices, grad_scores)
+    B, T, S, Hi, Di = _check_qkw(q, k, w)
+    if q.dtype == torch.float32 or Di != 64 or Hi > 4:
+        raise NotImplementedError("the indexer's backward kernels take bfloat16 / float16 operands with head_dim 64 and "
+                                  "at most 4 heads")
+    if topk_indices.dtype != torch.int32 or topk_indices.dim() != 3 or topk_indices.shape[:2] != (B, T):
+        raise ValueError("topk_indices must be int32 [B,T,k]")
+    K = topk_indices.shape[-1]
+    if tuple(grad_scores.shape) != (B, T, K):
+        raise ValueError(f"grad_scores must be [B,T,{K}], got {tuple(grad_scores.shape)}")
+    q, k, w, topk_indices = q.contiguous(), k.contiguous(), w.contiguous(), topk_indices.contiguous()
+    g = grad_scores.to(torch.float32).contiguous()
+    dq, dk, dw = torch.empty_like(q), torch.empty_like(k), torch.empty_like(w)
+    if T == 0 or K == 0:
+        return dq.zero_(), dk.zero_(), dw.zero_()
+    order, start = group_by_key(topk_indices, S)
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(Di)
+    lib = _lib.load()
+    ws = torch.empty(int(lib.gw_indexer_topk_bwd_workspace_bytes(B, T, S, K)), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.gw_indexer_topk_bwd(q.data_ptr(), k.data_ptr(), w.data_ptr(), topk_indices.data_ptr(), g.data_ptr(),
+                                     order.data_ptr(), start.data_ptr(), _lib.dtype_code(q), B, T, S, Hi, Di, K, scale,
+                                     dq.data_ptr(), dk.data_ptr(), dw.data_ptr(), ws.data_ptr(), ws.numel(),
+                                     _lib.status_word(dev).data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc, "gw_indexer_topk_bwd")
+    if _lib.debug_enabled():
+        _lib.check_status(dev)
+    return dq, dk, dw
+
+
+class _SparseTopkIndexer(torch.autograd.Function):
+    """The reference's ``SparseTopkIndexerFunc`` (:2047-2106): the selection itself runs without a graph, the returned
+    scores are differentiable in q, k and w."""
+
+    @staticmethod
+    def forward(ctx, q, k, w, topk, softmax_scale):
+        q, k, w = q.contiguous(), k.contiguous(), w.contiguous()
+        idx, sc = fused_score_topk(q, k, w, topk, softmax_scale, return_scores=True)
+        ctx.save_for_backward(q, k, w, idx)
+        ctx.softmax_scale = softmax_scale
+        ctx.mark_non_differentiable(idx)
+        ctx.set_materialize_grads(False)
+        return idx, sc
+
+    @staticmethod
+    def backward(ctx, grad_indices, grad_scores):
+        if grad_scores is None:
+            return None, None, None, None, None
+        q, k, w, idx = ctx.saved_tensors
+        dq, dk, dw = indexer_topk_backward(q, k, w, idx, grad_scores, ctx.softmax_scale)
+        return dq, dk, dw, None, None
+
+
 def sparse_topk_indexer_func(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, mask: Optional[torch.Tensor], topk: int,
                              softmax_scale: Optional[float], block_k: int, merge_blocks: int = 0,
                              view_bias_data: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Returns ``(topk_indices int32 [B,T,k], topk_scores q.dtype [B,T,k])``; forward only."""
+    """Returns ``(topk_indices int32 [B,T,k], topk_scores q.dtype [B,T,k])``.  With inputs that require grad the scores
+    are differentiable in q, k and w (16-bit operands); the selection itself is computed without a graph, as in the
+    reference (:2071)."""
     _reject_mask(mask, view_bias_data)
     if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or w.requires_grad):
-        q, k, w = q.detach(), k.detach(), w.detach()  # the reference computes the selection under no_grad (:2071)
+        if q.dtype == torch.float32:
+            raise NotImplementedError("the indexer's backward kernels take bfloat16 / float16 operands")
+        return _SparseTopkIndexer.apply(q, k, w, topk, softmax_scale)
     with torch.no_grad():
         return fused_score_topk(q, k, w, topk, softmax_scale, return_scores=True)
 

@@ -183,6 +183,23 @@ int gw_sparse_attn_bwd(const void* q, const void* k, const void* v, const int32_
                        void* workspace, size_t workspace_bytes, int* status_dev, gw_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Backward of the indexer's selected scores
+ *   score[t,j] = sum_h w[idx[t,j],h] * relu(scale * <q[t,h], k[idx[t,j],h]>)
+ * given grad_scores fp32 [B,T,K]: dq [B,T,Hi,Di], dk [B,S,Hi,Di], dw [B,S,Hi] of the operands' type.  q, k, w contiguous,
+ * GW_BF16 or GW_F16, Di = 64, Hi <= 4; topk_idx int32 [B,T,K], entries outside [0,S) carry no gradient.  key_order /
+ * key_start as for gw_sparse_attn_bwd (the lists stably sorted by key): no floating-point atomics, reproducible sums.
+ * workspace: gw_indexer_topk_bwd_workspace_bytes(B,T,S,K) bytes, 256-byte aligned.  Bounded waits report
+ * GW_ERR_TIMEOUT in status_dev (required).
+ * Replaces: easyvolcap/utils/custom_indexer/sparse_topk_indexer.py:757-895 (_backward_selected_topk_qkw) and its
+ *           Triton kernels :1847-2044 (fp32 atomic adds into dk and dw).
+ * ---------------------------------------------------------------------------------------------- */
+size_t gw_indexer_topk_bwd_workspace_bytes(int B, int T, int S, int K);
+int gw_indexer_topk_bwd(const void* q, const void* k, const void* w, const int32_t* topk_idx, const float* grad_scores,
+                        const int32_t* key_order, const int32_t* key_start, int dtype, int B, int T, int S, int Hi, int Di,
+                        int K, float scale, void* dq, void* dk, void* dw, void* workspace, size_t workspace_bytes,
+                        int* status_dev, gw_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Projection front-end (the step in front of stages 1-3): from the output of the layer's fused linear
  * projection to the six operator inputs, in one pass.
  *
