@@ -68,17 +68,21 @@ def indexer_cfg(topk: int = 1024, backend: str = "torch", kernel_dtype: str = "b
     return cfg
 
 
-def set_backend(block, model: str, views: int, backend: str, topk: int = 1024, kernel_dtype: str = "bfloat16") -> None:
-    """Switch an existing block between the torch and the kernel backend (the same weights serve both)."""
+def set_backend(block, model: str, views: int, backend: str, topk: int = 1024, kernel_dtype: str = "bfloat16", **state) -> None:
+    """Switch an existing block between the torch and the kernel backend (the same weights serve both).  ``state``:
+    further keys of the per-layer indexer state, e.g. the selector options ``source_downsample_enabled`` /
+    ``source_downsample_strategy`` / ``force_keep_special_tokens`` (``dsa_attention.py:3044-4277, 5042-5134``)."""
     from easyvolcap.utils.base_utils import dotdict
 
     cfg = indexer_cfg(topk, backend, kernel_dtype)
-    _, _, special = GRIDS[model]
+    gh, gw, special = GRIDS[model]
     block.attn.indexer_cfg = cfg
     block.attn.indexer.use_topk_kernel = bool(cfg.use_topk_kernel)
     block.attn.indexer.score_dtype = block.attn.indexer._parse_dtype(cfg.score_dtype)
     block.indexer_state = dotdict(cfg, enabled=True, warmup=False, sparse=True, compute_loss=False, layer_idx=9,
-                                  tokens_per_view=tokens_per_view(model), num_views=int(views), patch_start_idx=special)
+                                  tokens_per_view=tokens_per_view(model), num_views=int(views), patch_start_idx=special,
+                                  patch_grid_height=gh, patch_grid_width=gw)
+    block.indexer_state.update(state)
     block.return_indexer_loss = True  # as the aggregators do
 
 
