@@ -685,6 +685,19 @@ def run_micro(args):
                 "ms": ms, "bound": "hbm", "achieved": nbytes_bwd / ms / 1e6, "peak": hbm_peak, "unit": "GB/s",
                 "frac": nbytes_bwd / ms / 1e6 / hbm_peak})
     del o_f, lse_f, d_o
+    # the indexer's backward on the same lists: gradients of the selected scores for q_idx, k_idx and w
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_topk_backward
+    qi_ = torch.randn(1, T, HI, DI, device=dev).bfloat16()
+    ki_ = torch.randn(1, S, HI, DI, device=dev).bfloat16()
+    wi_ = torch.rand(1, S, HI, device=dev).bfloat16()
+    g_sc = torch.randn(1, T, TOPK, device=dev)
+    ms = timed(lambda: indexer_topk_backward(qi_, ki_, wi_, pos, g_sc, None), reps=3)
+    # per pair: the key's k_idx row and w, then from the key's side the q_idx row; the 32-byte scratch line written and read
+    nbytes_ib = T * TOPK * (2 * HI * DI * 2 + 16 + 2 * 32 + 4 + 4) + T * TOPK * 12
+    out.append({"op": "indexer backward (query kernel + key kernel + sort of the lists), bf16", "shape": [T, S, TOPK], "ms": ms,
+                "bound": "hbm", "achieved": nbytes_ib / ms / 1e6, "peak": hbm_peak, "unit": "GB/s",
+                "frac": nbytes_ib / ms / 1e6 / hbm_peak})
+    del qi_, ki_, wi_, g_sc
     # projection front-end on the benchmark's shape: 33 312 tokens, 16 heads + 4 indexer heads (VGGT grid positions)
     from geoweave_b200.front_end import FrontEndParams, project_epilogue, rope_tables
     del q, kk, vv, pos
