@@ -200,6 +200,23 @@ int gw_indexer_topk_bwd(const void* q, const void* k, const void* w, const int32
                         int* status_dev, gw_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Coarse-to-fine selection around the indexer (factor-2 pooled sources, round-robin expansion).
+ * source_to_fine int32 [L, width] (width <= 4): the tokens of every source, -1 for a missing slot, slots filled from the
+ * front.  gw_pool_sources: src_k [B,L,Hi,Di], src_w [B,L,Hi] = mean over a source's tokens of k [B,N,Hi,Di], w [B,N,Hi]
+ * (fp32 accumulation, result in `dtype`).  gw_expand_sources: per row (a query) a list of m kept sources and, optionally,
+ * their scores -> out_k token indices: sources ordered by descending score (equal scores: lower source first; without
+ * scores the given order is kept), then slot 0 of every source in that order, slot 1 of every source that has one, ...;
+ * cut to out_k; a list that yields fewer tokens is padded by cycling over its last pad_window tokens.  m, out_k <= 4096.
+ * Replaces: easyvolcap/official_vggt/layers/dsa_attention.py:3386-3543 (_prepare_source_downsample_projected, torch ops)
+ *           and :4079-4128 (_expand_source_downsample_chunk, torch ops; the reference keeps the order its unsorted top-k
+ *           returned).
+ * ---------------------------------------------------------------------------------------------- */
+int gw_pool_sources(const void* k, const void* w, const int32_t* source_to_fine, int dtype, int B, int N, int L, int Hi, int Di,
+                    int width, void* src_k, void* src_w, gw_stream_t stream);
+int gw_expand_sources(const int32_t* lists, const void* scores, int score_dtype, const int32_t* source_to_fine, int width, int L,
+                      int n_tokens, long long rows, int m, int out_k, int pad_window, int32_t* out, gw_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Projection front-end (the step in front of stages 1-3): from the output of the layer's fused linear
  * projection to the six operator inputs, in one pass.
  *

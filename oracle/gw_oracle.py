@@ -20,6 +20,10 @@ What each function follows (paths are relative to the reference project):
                           padding rule of the kernel path, easyvolcap/utils/custom_flash_attn/
                           sparse_index_flash_attn.py:208-218 (index < 0 or >= S contributes nothing), and the
                           ``attn_sum``/LSE side outputs of :375-458 and :250-252.
+* ``source_layout`` / ``coarse_topk`` / ``pool_sources`` / ``expand_sources``
+                          the coarse-to-fine selector of easyvolcap/official_vggt/layers/dsa_attention.py:3069-3258,
+                          3328-3375, 3386-3543, 4079-4128 (factor 2, "legacy" strategy: rank pooled 2x2 cells, expand the
+                          kept cells round-robin to tokens).
 * ``audit_topk``          the acceptance rule for a kernel that computes its own fp32 scores in a different
                           summation order: any index it picks that the oracle did not must sit within a
                           rounding bound of the oracle's k-th score.
@@ -40,6 +44,10 @@ __all__ = [
     "sparse_attention",
     "score_error_bound",
     "audit_topk",
+    "source_layout",
+    "coarse_topk",
+    "pool_sources",
+    "expand_sources",
 ]
 
 
@@ -302,3 +310,87 @@ def project_front_end(fused, pos, cos_tab, sin_tab, heads, head_dim, idx_heads, 
     iq = _rope_2d(iq, pos, cos_tab, sin_tab)
     ik = _rope_2d(norm(ik, idx_k_norm), pos, cos_tab, sin_tab)
     return q, k, v, iq, ik, w
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Coarse-to-fine selection (pooled sources), factor 2, round-robin expansion -- the reference's "legacy" strategy
+# ---------------------------------------------------------------------------------------------------------------------
+def source_layout(tokens_per_view: int, num_views: int, patch_start: int, grid_h: int, grid_w: int, factor: int = 2) -> dict:
+    """The list of "sources" the coarse stage ranks (dsa_attention.py:3069-3258, ``_get_source_downsample_layout``
+    without representative points): first every view's special tokens, then every patch token outside the pooled
+    region (``y >= pooled_h or x >= pooled_w``; view-major, row-major), then the ``factor x factor`` cells (view-major,
+    row-major), each with its fine tokens in row-major order.  ``source_to_fine`` is int64 ``[L, factor*factor]`` with
+    -1 for missing slots."""
+    assert tokens_per_view - patch_start == grid_h * grid_w
+    pooled_h, pooled_w = grid_h // factor * factor, grid_w // factor * factor
+    coarse_h, coarse_w = pooled_h // factor, pooled_w // factor
+    rows = []
+    for v in range(num_views):
+        rows += [[v * tokens_per_view + s] for s in range(patch_start)]
+    special = len(rows)
+    for v in range(num_views):
+        base = v * tokens_per_view + patch_start
+        rows += [[base + y * grid_w + x] for y in range(grid_h) for x in range(grid_w) if not (y < pooled_h and x < pooled_w)]
+    edge = len(rows) - special
+    for v in range(num_views):
+        base = v * tokens_per_view + patch_start
+        for cy in range(coarse_h):
+            for cx in range(coarse_w):
+                rows.append([base + (cy * factor + yy) * grid_w + cx * factor + xx for yy in range(factor) for xx in range(factor)])
+    width = factor * factor
+    table = torch.full((len(rows), width), -1, dtype=torch.int64)
+    for r, toks in enumerate(rows):
+        table[r, : len(toks)] = torch.tensor(toks)
+    coarse = len(rows) - special - edge
+    mapped = special + edge + coarse * width
+    return dict(source_to_fine=table, source_len=len(rows), special_count=special, edge_count=edge, coarse_count=coarse,
+                avg_expand=mapped / len(rows), non_special_source_len=len(rows) - special,
+                non_special_avg_expand=(mapped - special) / max(len(rows) - special, 1), factor=factor)
+
+
+def coarse_topk(layout: dict, topk: int, ratio: float = 1.1) -> int:
+    """How many sources the coarse stage keeps (dsa_attention.py:3328-3375 for the legacy strategy with
+    ``source_downsample_coarse_topk = 0``)."""
+    m = int(math.ceil(topk / max(layout["avg_expand"], 1.0) * max(ratio, 1.0)))
+    special = min(layout["special_count"], topk)
+    if 0 < special < topk and m < special and layout["non_special_source_len"] > 0:
+        rem = int(math.ceil((topk - special) / max(layout["non_special_avg_expand"], 1.0) * max(ratio, 1.0)))
+        m = max(m, special + max(rem, 1))
+    return min(max(m, 1), layout["source_len"])
+
+
+def pool_sources(k_idx, w, layout: dict):
+    """Keys and weights of the sources (dsa_attention.py:3386-3543): a special or edge source is its token, a cell is
+    the mean of its tokens (``avg_pool2d``), in fp32 here.  ``k_idx [B,N,Hi,Di]``, ``w [B,N,Hi]`` -> ``[B,L,Hi,Di]``,
+    ``[B,L,Hi]``."""
+    table = layout["source_to_fine"]
+    valid = table >= 0
+    safe = table.clamp_min(0)
+    kf, wf = _f32(k_idx), _f32(w)
+    cnt = valid.sum(-1).to(torch.float32)
+    ks = (kf[:, safe] * valid[None, :, :, None, None]).sum(2) / cnt[None, :, None, None]
+    ws = (wf[:, safe] * valid[None, :, :, None]).sum(2) / cnt[None, :, None]
+    return ks, ws
+
+
+def expand_sources(coarse_idx, layout: dict, topk: int, fine_len: int, pad_window: int = 64) -> torch.Tensor:
+    """From each query's ORDERED list of sources to ``min(topk, fine_len)`` token indices (dsa_attention.py:4079-4128,
+    round-robin form): slot 0 of every listed source in list order, then slot 1 of every source that has one, and so
+    on; cut to the target length; a list that is too short is padded by cycling over its last ``pad_window`` entries."""
+    table = layout["source_to_fine"]
+    B, T, m = coarse_idx.shape
+    target = min(int(topk), int(fine_len))
+    out = torch.empty((B, T, target), dtype=torch.int64)
+    for b in range(B):
+        for t in range(T):
+            blocks = table[coarse_idx[b, t].long()]                      # [m, width]
+            flat = blocks.t().reshape(-1)                                # slot-major
+            toks = flat[flat >= 0][:target]
+            n = max(int(toks.numel()), 1)
+            if toks.numel() < target:
+                win = min(n, max(1, min(int(pad_window), target)))
+                start = n - win
+                pad = torch.tensor([int(toks[start + (i % win)]) for i in range(target - toks.numel())], dtype=torch.int64)
+                toks = torch.cat([toks, pad])
+            out[b, t] = toks
+    return out

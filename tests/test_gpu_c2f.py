@@ -1,0 +1,100 @@
+"""GPU parity of the coarse-to-fine selection: pooled sources and expansion against the reference's own outputs
+(``tests/golden/reference_c2f.npz``) and, on larger seeded inputs, against the oracle; the whole selection against the
+oracle's pipeline; the layer with pooled sources."""
+import numpy as np
+import pytest
+import torch
+
+import geoweave_b200
+from geoweave_b200.coarse_to_fine import expand_sources, pool_sources, select_topk_coarse_to_fine, source_layout
+from oracle import gw_oracle as orc
+from tests import golden
+from tests.golden.make_golden_c2f import CASES
+from tests.gpu_util import dev
+
+pytestmark = pytest.mark.gpu
+GOLD = golden.load("reference_c2f.npz")
+
+
+@pytest.mark.parametrize("name", [n for n in sorted(CASES) if CASES[n][7]])
+def test_pooled_sources_match_the_reference(name):
+    tpv, views, special, gh, gw, _, _, _ = CASES[name]
+    lay = source_layout(tpv, views, special, gh, gw, dev())
+    g = GOLD[name]
+    k, w = torch.from_numpy(g["k"]).to(dev()), torch.from_numpy(g["w"]).to(dev())
+    sk, sw = pool_sources(k, w, lay)                           # fp32 in, fp32 out
+    assert np.allclose(sk.cpu().numpy(), g["src_k"], rtol=0, atol=1e-6) and np.allclose(sw.cpu().numpy(), g["src_w"], rtol=0, atol=1e-6)
+    for dt in (torch.bfloat16, torch.float16):                 # 16-bit in (exactly representable), mean rounded once
+        sk, sw = pool_sources(k.to(dt), w.to(dt), lay)
+        ref_k, ref_w = torch.from_numpy(g["src_k"]).to(dt), torch.from_numpy(g["src_w"]).to(dt)
+        if dt == torch.bfloat16:
+            assert torch.equal(sk.cpu(), ref_k) and torch.equal(sw.cpu(), ref_w)
+        else:  # the fixture's inputs are bf16 values, not all exact in fp16
+            kk, ww = orc.pool_sources(k.to(dt).cpu(), w.to(dt).cpu(), orc.source_layout(tpv, views, special, gh, gw))
+            assert torch.equal(sk.cpu(), kk.to(dt)) and torch.equal(sw.cpu(), ww.to(dt))
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_expansion_in_the_given_order_matches_the_reference(name):
+    tpv, views, special, gh, gw, topk, _, _ = CASES[name]
+    lay = source_layout(tpv, views, special, gh, gw, dev())
+    g = GOLD[name]
+    fine = expand_sources(torch.from_numpy(g["lists"]).to(dev()), None, lay, topk)
+    assert fine.dtype == torch.int32 and np.array_equal(fine.cpu().numpy(), g["fine"])
+
+
+@pytest.mark.parametrize("tpv,views,special,gh,gw,topk,m,dt", [
+    (5 + 28 * 37, 3, 5, 28, 37, 1024, 300, torch.bfloat16),
+    (5 + 21 * 37, 2, 5, 21, 37, 512, 149, torch.float32),
+    (2 + 5 * 7, 2, 2, 5, 7, 60, 11, torch.float16),            # short lists: padded
+    (1 + 6 * 6, 4, 1, 6, 6, 100, 40, torch.bfloat16),          # more tokens than wanted: cut inside a slot round
+])
+def test_expansion_by_descending_score(tpv, views, special, gh, gw, topk, m, dt):
+    lay = source_layout(tpv, views, special, gh, gw, dev())
+    olay = orc.source_layout(tpv, views, special, gh, gw)
+    g = torch.Generator().manual_seed(m)
+    T = 70
+    lists = torch.stack([torch.stack([torch.randperm(lay.source_len, generator=g)[:m] for _ in range(T)]) for _ in range(2)]).to(torch.int32)
+    scores = (torch.randn(2, T, m, generator=g) * 3).round().div(2).to(dt)   # many equal scores
+    fine = expand_sources(lists.to(dev()), scores.to(dev()), lay, topk)
+    # oracle: stable sort by (score descending, source ascending), then the reference's expansion of the ordered list
+    by_src = torch.argsort(lists.long(), dim=-1, stable=True)
+    l1, s1 = torch.gather(lists.long(), -1, by_src), torch.gather(scores.float(), -1, by_src)
+    by_score = torch.argsort(s1, dim=-1, descending=True, stable=True)
+    ordered = torch.gather(l1, -1, by_score)
+    want = orc.expand_sources(ordered, olay, topk, tpv * views)
+    assert torch.equal(fine.cpu().long(), want)
+
+
+def test_whole_selection_against_the_oracle_pipeline():
+    tpv, views, special, gh, gw, topk = 5 + 28 * 37, 2, 5, 28, 37, 256
+    lay = source_layout(tpv, views, special, gh, gw, dev())
+    olay = orc.source_layout(tpv, views, special, gh, gw)
+    N = tpv * views
+    g = torch.Generator().manual_seed(7)
+    q = torch.randn(1, N, 4, 64, generator=g).bfloat16()
+    k = torch.randn(1, N, 4, 64, generator=g).bfloat16()
+    w = torch.rand(1, N, 4, generator=g).bfloat16()
+    idx = select_topk_coarse_to_fine(q.to(dev()), k.to(dev()), w.to(dev()), lay, topk, 0.125)
+    geoweave_b200.check_status()
+    assert tuple(idx.shape) == (1, N, topk) and int(idx.min()) >= 0 and int(idx.max()) < N
+    # stage by stage with the oracle: pooled sources (rounded to bf16 as the kernel stores them), exact top-m of the
+    # oracle's scores, expansion by descending score
+    sk, sw = orc.pool_sources(k, w, olay)
+    sk, sw = sk.bfloat16(), sw.bfloat16()
+    m = lay.kept_sources(topk)
+    assert m == orc.coarse_topk(olay, topk)
+    rows = torch.arange(0, N, 9)
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import fused_score_topk
+    kept, sc = fused_score_topk(q.to(dev())[:, rows.to(dev())], sk.to(dev()), sw.to(dev()), m, 0.125, return_scores=True)
+    scores = orc.indexer_scores(q[:, rows], sk, sw, 0.125)
+    res = orc.audit_topk(kept.cpu(), scores, m, q[:, rows], sk, sw, 0.125)
+    assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res
+    by_src = torch.argsort(kept.cpu().long(), dim=-1, stable=True)
+    l1, s1 = torch.gather(kept.cpu().long(), -1, by_src), torch.gather(sc.cpu().float(), -1, by_src)
+    ordered = torch.gather(l1, -1, torch.argsort(s1, dim=-1, descending=True, stable=True))
+    want = orc.expand_sources(ordered, olay, topk, N)
+    assert torch.equal(idx.cpu()[:, rows].long(), want)
+    # every row lists distinct tokens (the lists are long enough here that nothing is padded)
+    srt = torch.sort(idx[0].long(), -1).values
+    assert bool((srt[:, 1:] != srt[:, :-1]).all())
