@@ -459,6 +459,23 @@ def run_ours(args):
         ctx_clk = ctx_clocks.stop(t0c, time.perf_counter()) if ctx_clocks else None
         ctx = {"ms": ms_ctx, "idx_ms": statistics.mean(a.elapsed_time(b) for a, b, _ in ctx_events),
                "att_ms": statistics.mean(b.elapsed_time(c) for _, b, c in ctx_events), "rows": chi - clo, "tokens": n_ctx, "clocks": ctx_clk}
+        if world == 1:
+            # the selection stage alone, coarse-to-fine (2x2-pooled sources, kept cells expanded) against the full-resolution
+            # indexer call, on this context and on the main workload's 32 views
+            from geoweave_b200.coarse_to_fine import select_topk_coarse_to_fine, source_layout
+            from geoweave_b200.custom_indexer.sparse_topk_indexer import fused_score_topk
+
+            c2f = {}
+            for tag, n_views, src in (("ctx256", 256, tc), ("vggt32", views, resident[0])):
+                lay = source_layout(1041, n_views, 5, 28, 37, dev)
+                nn = 1041 * n_views
+                f_c2f = lambda: select_topk_coarse_to_fine(src["q_idx"], src["k_idx"], src["w"], lay, TOPK, DI ** -0.5)
+                f_full = lambda: fused_score_topk(src["q_idx"], src["k_idx"], src["w"], TOPK, DI ** -0.5, return_scores=False)
+                f_c2f(), f_full()
+                c2f[tag] = {"tokens": nn, "sources": lay.source_len, "kept_sources": lay.kept_sources(TOPK),
+                            "coarse_to_fine_ms": timed(f_c2f, 3) / 3, "full_indexer_ms": timed(f_full, 3) / 3}
+            ctx["c2f"] = c2f
+            geoweave_b200.check_status()
         del tc
         last.clear()
         torch.cuda.empty_cache()
@@ -561,6 +578,11 @@ def run_ours(args):
                 "attention_ms": ctx["att_ms"], "indexer_tflops": cf / (ctx["idx_ms"] * 1e-3) / 1e12,
                 "indexer_frac": cf / (ctx["idx_ms"] * 1e-3) / 1e12 / tc_peak,
                 "attention_gbs": attn_bytes_of(ctx["rows"]) / (ctx["att_ms"] * 1e-3) / 1e9, "steps": 2, "warmup": 1, "clocks": ctx["clocks"]}
+        if ctx and "c2f" in ctx:
+            line["coarse_to_fine_selection"] = dict(ctx["c2f"], note="selection stage alone (one call, CUDA events): pooled 2x2 "
+                                                    "sources -> fused indexer over the sources -> expansion to 1024 tokens, against the "
+                                                    "full-resolution fused indexer on the same inputs; random inputs, so only the cost "
+                                                    "is meaningful here, not which tokens are found")
         if proj is not None:
             if "ms_per_layer" in proj:
                 proj["indexer_frac"] = idx_flops / (proj["idx_ms"] * 1e-3) / 1e12 / tc_peak

@@ -5,6 +5,9 @@ This is the composition the reference's fastest configuration runs per layer
 (``easyvolcap/official_vggt/layers/dsa_attention.py:1495-1675``, "full-chain" path) together with its cross-layer
 reuse of top-k indices (``easyvolcap/official_vggt/models/aggregator.py:390-423, 681-694``: a layer listed in
 ``reuse_topk_source_by_layer`` takes the indices its source layer selected and skips its own indexer).
+With a ``source_layout`` the indexer stage is the coarse-to-fine selection (``geoweave_b200.coarse_to_fine``): 2x2-pooled
+patch cells are ranked and the kept cells expanded to tokens (the reference's ``source_downsample_enabled``,
+``dsa_attention.py:1534-1556``).
 The output projection, MLP and residuals around it are row-local model code and stay with the caller.
 """
 from __future__ import annotations
@@ -15,6 +18,7 @@ import torch
 
 from . import _lib
 from .custom_flash_attn.sparse_index_flash_attn import sparse_index_flash_attn_inference_func
+from .coarse_to_fine import SourceLayout, select_topk_coarse_to_fine
 from .custom_indexer.sparse_topk_indexer import fused_score_topk, indexer_workspace_bytes
 from .front_end import HEAD_DIM, FrontEndParams, project_qkv_and_indexer
 
@@ -26,11 +30,14 @@ class SparseGlobalAttentionLayer:
     still part of the one GEMM, as in the reference, whose fused weight is cached per layer).
     ``use_cuda_graph``: the chain is captured once per (shape, dtype, reuse or not) and replayed; inputs are copied
     into the graph's own buffers and the results are views of buffers that the next call overwrites.
+    ``source_layout``: select coarse-to-fine over this layout's pooled sources instead of over all tokens.
     """
 
     def __init__(self, params: FrontEndParams, topk: int, idx_scale: Optional[float] = None,
-                 attn_scale: Optional[float] = None, use_cuda_graph: bool = False):
+                 attn_scale: Optional[float] = None, use_cuda_graph: bool = False,
+                 source_layout: Optional[SourceLayout] = None):
         self.params = params
+        self.source_layout = source_layout
         self.topk = int(topk)
         self.idx_scale = float(idx_scale) if idx_scale is not None else HEAD_DIM ** -0.5
         self.attn_scale = float(attn_scale) if attn_scale is not None else HEAD_DIM ** -0.5
@@ -42,8 +49,12 @@ class SparseGlobalAttentionLayer:
         q, k, v, q_idx, k_idx, w = project_qkv_and_indexer(x, pos, self.params)
         if reuse_idx is None:
             with torch.inference_mode():
-                idx, _ = fused_score_topk(q_idx, k_idx, w, min(self.topk, x.shape[1]), self.idx_scale, return_scores=False,
-                                          workspace=workspace)
+                if self.source_layout is not None:
+                    idx = select_topk_coarse_to_fine(q_idx, k_idx, w, self.source_layout, min(self.topk, x.shape[1]),
+                                                     self.idx_scale, workspace=workspace)
+                else:
+                    idx, _ = fused_score_topk(q_idx, k_idx, w, min(self.topk, x.shape[1]), self.idx_scale, return_scores=False,
+                                              workspace=workspace)
         else:
             idx = reuse_idx
         out, _ = sparse_index_flash_attn_inference_func(q, k, v, idx, None, False, self.attn_scale)
@@ -79,7 +90,11 @@ class SparseGlobalAttentionLayer:
             # the graph records raw pointers, so it owns its indexer workspace: a buffer from the shared cache could
             # be replaced (a larger shape, clear_runtime_cache) while the graph is still replayed
             B, N = x.shape[:2]
-            nbytes = indexer_workspace_bytes(B, N, N, self.params.idx_heads, HEAD_DIM, min(self.topk, N))
+            if self.source_layout is not None:
+                lay = self.source_layout
+                nbytes = indexer_workspace_bytes(B, N, lay.source_len, self.params.idx_heads, HEAD_DIM, lay.kept_sources(min(self.topk, N)))
+            else:
+                nbytes = indexer_workspace_bytes(B, N, N, self.params.idx_heads, HEAD_DIM, min(self.topk, N))
             st["ws"] = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=x.device)
         side = torch.cuda.Stream(device=x.device)
         side.wait_stream(torch.cuda.current_stream(x.device))

@@ -95,6 +95,40 @@ def test_whole_selection_against_the_oracle_pipeline():
     ordered = torch.gather(l1, -1, torch.argsort(s1, dim=-1, descending=True, stable=True))
     want = orc.expand_sources(ordered, olay, topk, N)
     assert torch.equal(idx.cpu()[:, rows].long(), want)
-    # every row lists distinct tokens (the lists are long enough here that nothing is padded)
-    srt = torch.sort(idx[0].long(), -1).values
-    assert bool((srt[:, 1:] != srt[:, :-1]).all())
+
+
+def test_layer_with_pooled_sources_eager_and_graph():
+    """The whole layer with a source layout: the indices are what the coarse-to-fine selection gives on the layer's own
+    projections, the CUDA-graph replay gives what the eager chain gives, and the output is the attention over them."""
+    from geoweave_b200.front_end import FrontEndParams, project_qkv_and_indexer, rope_tables
+    from geoweave_b200.layer import SparseGlobalAttentionLayer
+
+    g = torch.Generator().manual_seed(17)
+    tpv, views, special, gh, gw = 5 + 28 * 37, 4, 5, 28, 37
+    N, heads, dim, k = tpv * views, 16, 256, 512
+    lay = source_layout(tpv, views, special, gh, gw, dev())
+    width = 3 * heads * 64 + 2 * 4 * 64 + 4
+    weight = (torch.randn(width, dim, generator=g) * dim ** -0.5).bfloat16().to(dev())
+    cos, sin = rope_tables(40, dev(), torch.bfloat16)
+    vec = lambda: ((torch.rand(64, generator=g) + 0.5).to(dev()), (torch.randn(64, generator=g) * 0.1).to(dev()), 1e-5)
+    prm = FrontEndParams(weight, None, heads, 4, vec(), vec(), vec(), cos, sin)
+    eager = SparseGlobalAttentionLayer(prm, k, source_layout=lay)
+    graphed = SparseGlobalAttentionLayer(prm, k, use_cuda_graph=True, source_layout=lay)
+    x = torch.randn(1, N, dim, generator=g).bfloat16().to(dev())
+    ys, xs = torch.meshgrid(torch.arange(gh), torch.arange(gw), indexing="ij")
+    grid = torch.stack([ys.reshape(-1), xs.reshape(-1)], -1) + 1
+    pos = torch.cat([torch.zeros(special, 2, dtype=torch.long), grid]).repeat(views, 1).view(1, N, 2).to(dev())
+    for trial in range(2):
+        out_e, idx_e = eager(x, pos)
+        out_g, idx_g = graphed(x, pos)
+        geoweave_b200.check_status()
+        assert idx_e.shape == (1, N, k) and torch.equal(idx_e, idx_g)   # the expansion fixes the order too
+        assert (out_e.float() - out_g.float()).abs().max().item() <= 2e-2
+        x = x.roll(1, 1)
+    q, kk, v, qi, ki, w = project_qkv_and_indexer(x.roll(-1, 1), pos, prm)
+    want = select_topk_coarse_to_fine(qi, ki, w, lay, k, 0.125)
+    assert torch.equal(want, idx_g)
+    rows = torch.arange(0, N, 97)
+    ref_out, _, _ = orc.sparse_attention(q.cpu()[:, rows], kk.cpu(), v.cpu(), idx_g[:, rows.to(dev())].cpu(), 0.125)
+    got = out_g.view(1, N, heads, 64)[:, rows.to(dev())].float().cpu()
+    assert (got - ref_out).abs().max().item() <= 2e-2
