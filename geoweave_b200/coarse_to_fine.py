@@ -40,6 +40,7 @@ class SourceLayout:
     edge_count: int           # patch tokens outside the pooled region (an odd last row / column)
     coarse_count: int         # 2x2 cells
     table: torch.Tensor       # int32 [source_len, 4] on the device: tokens of every source, -1 = no such slot
+    token_source: torch.Tensor  # int64 [n_tokens] on the device: the source every token belongs to
 
     @property
     def source_len(self) -> int:
@@ -91,28 +92,33 @@ def source_layout(tokens_per_view: int, num_views: int, patch_start: int, grid_h
     table[: special.numel(), 0] = special
     table[special.numel(): special.numel() + edge.numel(), 0] = edge
     table[special.numel() + edge.numel():] = cells
+    token_source = torch.empty(tokens_per_view * num_views, dtype=torch.int64)
+    rows = torch.arange(table.shape[0]).view(-1, 1).expand_as(table)
+    token_source[table[table >= 0]] = rows[table >= 0]
     lay = SourceLayout(tokens_per_view, num_views, patch_start, grid_h, grid_w, int(special.numel()), int(edge.numel()),
-                       int(cells.shape[0]), table.to(torch.int32).to(device).contiguous())
+                       int(cells.shape[0]), table.to(torch.int32).to(device).contiguous(), token_source.to(device))
     _LAYOUTS[key] = lay
     return lay
 
 
-def pool_sources(k_idx: torch.Tensor, w: torch.Tensor, layout: SourceLayout) -> Tuple[torch.Tensor, torch.Tensor]:
+def pool_sources(k_idx: torch.Tensor, w: Optional[torch.Tensor], layout: SourceLayout) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """``k_idx [B,N,Hi,Di]``, ``w [B,N,Hi]`` -> the sources' keys ``[B,L,Hi,Di]`` and weights ``[B,L,Hi]``
-    (``_prepare_source_downsample_projected``, :3386-3543)."""
-    dev = _lib.require_cuda(k_idx, w)
+    (``_prepare_source_downsample_projected``, :3386-3543).  With ``w`` None only the first is made -- the same mean
+    applied to the queries (``_prepare_query_downsample_chunk``, :3925-3994, for a chunk that holds whole sources)."""
+    dev = _lib.require_cuda(k_idx) if w is None else _lib.require_cuda(k_idx, w)
     B, N, Hi, Di = k_idx.shape
-    if N != layout.n_tokens or tuple(w.shape) != (B, N, Hi) or w.dtype != k_idx.dtype:
-        raise ValueError(f"k_idx {tuple(k_idx.shape)} / w {tuple(w.shape)} do not match a layout of {layout.n_tokens} tokens")
+    if N != layout.n_tokens or (w is not None and (tuple(w.shape) != (B, N, Hi) or w.dtype != k_idx.dtype)):
+        raise ValueError(f"k_idx {tuple(k_idx.shape)} / w do not match a layout of {layout.n_tokens} tokens")
     if layout.table.device != dev:
         raise ValueError("the layout was built for another device")
-    k_idx, w = k_idx.contiguous(), w.contiguous()
+    k_idx = k_idx.contiguous()
+    w = None if w is None else w.contiguous()
     L = layout.source_len
     src_k = torch.empty((B, L, Hi, Di), device=dev, dtype=k_idx.dtype)
-    src_w = torch.empty((B, L, Hi), device=dev, dtype=w.dtype)
+    src_w = None if w is None else torch.empty((B, L, Hi), device=dev, dtype=w.dtype)
     with torch.cuda.device(dev):
-        rc = _lib.load().gw_pool_sources(k_idx.data_ptr(), w.data_ptr(), layout.table.data_ptr(), _lib.dtype_code(k_idx), B, N, L, Hi,
-                                         Di, 4, src_k.data_ptr(), src_w.data_ptr(), _lib.stream_ptr(dev))
+        rc = _lib.load().gw_pool_sources(k_idx.data_ptr(), _lib.ptr(w), layout.table.data_ptr(), _lib.dtype_code(k_idx), B, N, L, Hi,
+                                         Di, 4, src_k.data_ptr(), _lib.ptr(src_w), _lib.stream_ptr(dev))
     _lib.check(rc, "gw_pool_sources")
     return src_k, src_w
 
@@ -143,11 +149,20 @@ def expand_sources(kept: torch.Tensor, scores: Optional[torch.Tensor], layout: S
 
 def select_topk_coarse_to_fine(q_idx: torch.Tensor, k_idx: torch.Tensor, w: torch.Tensor, layout: SourceLayout, topk: int,
                                softmax_scale: Optional[float] = None, ratio: float = 1.1, pad_window: int = 64,
-                               workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                               workspace: Optional[torch.Tensor] = None, pool_queries: bool = False) -> torch.Tensor:
     """The selection of a layer with pooled sources: int32 ``[B,T,min(topk,N)]`` token indices per query
-    (``_select_topk_source_downsample_chunk``, strategy ``legacy``, :4187-4224).  ``q_idx [B,T,Hi,Di]`` may be any block
-    of query rows; ``k_idx`` / ``w`` are all N tokens of the layout."""
+    (``_select_topk_source_downsample_chunk``, :4187-4224).  ``k_idx`` / ``w`` are all N tokens of the layout.
+
+    ``pool_queries=False`` (strategy ``legacy``): ``q_idx [B,T,Hi,Di]`` may be any block of query rows, each scored
+    against the sources.  ``pool_queries=True`` (strategy ``qk_sym_x2_broadcast``, :4019-4077): the queries are pooled like
+    the keys, one list is selected per source and every token takes the list of its source; ``q_idx`` must then be all N
+    tokens."""
     src_k, src_w = pool_sources(k_idx, w, layout)
     m = layout.kept_sources(min(int(topk), layout.n_tokens), ratio)
-    kept, scores = fused_score_topk(q_idx, src_k, src_w, m, softmax_scale, return_scores=True, workspace=workspace)
-    return expand_sources(kept, scores, layout, topk, pad_window)
+    if not pool_queries:
+        kept, scores = fused_score_topk(q_idx, src_k, src_w, m, softmax_scale, return_scores=True, workspace=workspace)
+        return expand_sources(kept, scores, layout, topk, pad_window)
+    src_q, _ = pool_sources(q_idx, None, layout)
+    kept, scores = fused_score_topk(src_q, src_k, src_w, m, softmax_scale, return_scores=True, workspace=workspace)
+    lists = expand_sources(kept, scores, layout, topk, pad_window)          # [B,L,topk]
+    return lists.index_select(1, layout.token_source)                       # (:3996-4017)

@@ -77,6 +77,12 @@ struct BwdMmaParams {
   float scale;
 };
 
+// a producer that leaves after a timeout lets the copies it started land first (bounded), so that none arrives in
+// shared memory the CTA has already given up
+__device__ __forceinline__ void bm_drain(uint64_t* full, uint32_t it) {
+  for (uint32_t u = it > BM_NB ? it - BM_NB : 0u; u < it; ++u) mbar_wait_limit(&full[u % BM_NB], (u / BM_NB) & 1u, kDrainLimitNs);
+}
+
 __device__ __forceinline__ void bm_init_barriers(BmShared* sh) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < BM_NB; ++s) {
@@ -127,6 +133,7 @@ __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_query_mma_kernel(const
         const uint32_t mask = __ballot_sync(0xffffffffu, valid) & ((1u << BM_KPP) - 1u);
         const uint32_t slot = it % BM_NB;
         if (!mbar_wait_bounded(&sh->empty[slot], ((it / BM_NB) & 1u) ^ 1u)) {
+          bm_drain(sh->full, it);
           report_status(p.status, GW_ERR_TIMEOUT);
           return;
         }
@@ -299,6 +306,7 @@ __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_key_mma_kernel(const B
         const long long tq = f / K;
         const uint32_t slot = it % BM_NB;
         if (!mbar_wait_bounded(&sh->empty[slot], ((it / BM_NB) & 1u) ^ 1u)) {
+          bm_drain(sh->full, it);
           report_status(p.status, GW_ERR_TIMEOUT);
           return;
         }

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(256) pool_sources_kernel(const T* __restrict__
     for (int i = 0; i < VEC; ++i) o[i] = from_float<T>(acc[i] * inv);
     *reinterpret_cast<uint4*>(ko + e) = out;
   }
-  if (lane < Hi) {
+  if (w != nullptr && lane < Hi) {
     float acc = 0.f;
     for (int c = 0; c < cnt; ++c) acc += to_float(w[(b * N + tok[c]) * Hi + lane]);
     src_w[(b * L + r) * Hi + lane] = from_float<T>(acc * inv);
@@ -162,7 +162,7 @@ using namespace gw;
 
 extern "C" int gw_pool_sources(const void* k, const void* w, const int32_t* source_to_fine, int dtype, int B, int N, int L, int Hi,
                                int Di, int width, void* src_k, void* src_w, gw_stream_t stream) {
-  if (!k || !w || !source_to_fine || !src_k || !src_w) return GW_ERR_INVALID_ARG;
+  if (!k || !source_to_fine || !src_k || (w != nullptr) != (src_w != nullptr)) return GW_ERR_INVALID_ARG;  // w is optional
   if (B <= 0 || N <= 0 || L <= 0 || Hi <= 0 || Di <= 0 || B > 65535) return GW_ERR_INVALID_ARG;
   if (width < 1 || width > C2F_MAX_WIDTH || Hi > 32) return GW_ERR_UNSUPPORTED;
   const size_t es = dtype_size(dtype);

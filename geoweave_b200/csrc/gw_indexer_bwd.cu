@@ -89,6 +89,12 @@ __global__ void ib_prepare_w_kernel(const T* __restrict__ w, float* __restrict__
   reinterpret_cast<float4*>(wtab)[i] = o;
 }
 
+// a producer that leaves after a timeout lets the copies it started land first (bounded), so that none arrives in
+// shared memory the CTA has already given up
+__device__ __forceinline__ void ib_drain(uint64_t* full, uint32_t it) {
+  for (uint32_t u = it > IB_NB ? it - IB_NB : 0u; u < it; ++u) mbar_wait_limit(&full[u % IB_NB], (u / IB_NB) & 1u, kDrainLimitNs);
+}
+
 template <int HI>
 __device__ __forceinline__ void ib_init_barriers(IbShared* sh) {
   if (threadIdx.x == 0) {
@@ -136,6 +142,7 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_que
         const uint32_t mask = __ballot_sync(0xffffffffu, valid) & 0xffffu;
         const uint32_t slot = it % IB_NB;
         if (!mbar_wait_bounded(&sh->empty[slot], ((it / IB_NB) & 1u) ^ 1u)) {
+          ib_drain(sh->full, it);
           report_status(p.status, GW_ERR_TIMEOUT);
           return;
         }
@@ -276,6 +283,7 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_key
         const long long tq = f / K;
         const uint32_t slot = it % IB_NB;
         if (!mbar_wait_bounded(&sh->empty[slot], ((it / IB_NB) & 1u) ^ 1u)) {
+          ib_drain(sh->full, it);
           report_status(p.status, GW_ERR_TIMEOUT);
           return;
         }

@@ -30,14 +30,16 @@ class SparseGlobalAttentionLayer:
     still part of the one GEMM, as in the reference, whose fused weight is cached per layer).
     ``use_cuda_graph``: the chain is captured once per (shape, dtype, reuse or not) and replayed; inputs are copied
     into the graph's own buffers and the results are views of buffers that the next call overwrites.
-    ``source_layout``: select coarse-to-fine over this layout's pooled sources instead of over all tokens.
+    ``source_layout``: select coarse-to-fine over this layout's pooled sources instead of over all tokens;
+    ``pool_queries``: pool the queries too and give every token the list of its cell.
     """
 
     def __init__(self, params: FrontEndParams, topk: int, idx_scale: Optional[float] = None,
                  attn_scale: Optional[float] = None, use_cuda_graph: bool = False,
-                 source_layout: Optional[SourceLayout] = None):
+                 source_layout: Optional[SourceLayout] = None, pool_queries: bool = False):
         self.params = params
         self.source_layout = source_layout
+        self.pool_queries = bool(pool_queries)
         self.topk = int(topk)
         self.idx_scale = float(idx_scale) if idx_scale is not None else HEAD_DIM ** -0.5
         self.attn_scale = float(attn_scale) if attn_scale is not None else HEAD_DIM ** -0.5
@@ -51,7 +53,7 @@ class SparseGlobalAttentionLayer:
             with torch.inference_mode():
                 if self.source_layout is not None:
                     idx = select_topk_coarse_to_fine(q_idx, k_idx, w, self.source_layout, min(self.topk, x.shape[1]),
-                                                     self.idx_scale, workspace=workspace)
+                                                     self.idx_scale, workspace=workspace, pool_queries=self.pool_queries)
                 else:
                     idx, _ = fused_score_topk(q_idx, k_idx, w, min(self.topk, x.shape[1]), self.idx_scale, return_scores=False,
                                               workspace=workspace)

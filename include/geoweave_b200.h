@@ -203,7 +203,8 @@ int gw_indexer_topk_bwd(const void* q, const void* k, const void* w, const int32
  * Coarse-to-fine selection around the indexer (factor-2 pooled sources, round-robin expansion).
  * source_to_fine int32 [L, width] (width <= 4): the tokens of every source, -1 for a missing slot, slots filled from the
  * front.  gw_pool_sources: src_k [B,L,Hi,Di], src_w [B,L,Hi] = mean over a source's tokens of k [B,N,Hi,Di], w [B,N,Hi]
- * (fp32 accumulation, result in `dtype`).  gw_expand_sources: per row (a query) a list of m kept sources and, optionally,
+ * (fp32 accumulation, result in `dtype`; w and src_w may both be null: keys only, e.g. to pool queries the same way).
+ * gw_expand_sources: per row (a query) a list of m kept sources and, optionally,
  * their scores -> out_k token indices: sources ordered by descending score (equal scores: lower source first; without
  * scores the given order is kept), then slot 0 of every source in that order, slot 1 of every source that has one, ...;
  * cut to out_k; a list that yields fewer tokens is padded by cycling over its last pad_window tokens.  m, out_k <= 4096.

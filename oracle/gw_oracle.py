@@ -45,6 +45,7 @@ __all__ = [
     "score_error_bound",
     "audit_topk",
     "source_layout",
+    "token_source",
     "coarse_topk",
     "pool_sources",
     "expand_sources",
@@ -346,6 +347,16 @@ def source_layout(tokens_per_view: int, num_views: int, patch_start: int, grid_h
     return dict(source_to_fine=table, source_len=len(rows), special_count=special, edge_count=edge, coarse_count=coarse,
                 avg_expand=mapped / len(rows), non_special_source_len=len(rows) - special,
                 non_special_avg_expand=(mapped - special) / max(len(rows) - special, 1), factor=factor)
+
+
+def token_source(layout: dict) -> torch.Tensor:
+    """int64 [N]: the source each token belongs to (``fine_to_source_row``, dsa_attention.py:3186-3196); with pooled
+    queries every token takes the list selected for that source (:3996-4017)."""
+    table = layout["source_to_fine"]
+    out = torch.full((int(table.max()) + 1,), -1, dtype=torch.int64)
+    rows = torch.arange(table.shape[0]).view(-1, 1).expand_as(table)
+    out[table[table >= 0]] = rows[table >= 0]
+    return out
 
 
 def coarse_topk(layout: dict, topk: int, ratio: float = 1.1) -> int:

@@ -8,6 +8,8 @@ Recorded per case (all produced by reference code, ``easyvolcap/official_vggt/la
                           coarse) -- plus ``coarse_topk`` from ``_resolve_source_downsample_coarse_topk`` (:3328-3375)
 * ``src_k``, ``src_w``    ``_prepare_source_downsample_projected`` (:3386-3543) on seeded bf16-representable fp32 inputs
 * ``fine``                ``_expand_source_downsample_chunk`` (:4079-4128) on seeded ordered lists of distinct sources
+* ``coarse_q``, ``fine_to_row``  ``_prepare_query_downsample_chunk`` (:3925-3994) with the whole sequence as one chunk: the
+                          pooled queries and, per token, the row of the list it takes (qk_sym_x2_broadcast)
 """
 import argparse
 import os
@@ -59,6 +61,9 @@ def main():
             out[f"{name}.w:bf16"] = (w.view(torch.int32).numpy() >> 16).astype(np.int16)
             out[f"{name}.src_k"] = prep.source_k.numpy()
             out[f"{name}.src_w"] = prep.source_w.numpy()
+            qp = attn._prepare_query_downsample_chunk(k, layout, 0)     # the same tensor taken as queries, one chunk
+            out[f"{name}.coarse_q"] = qp.coarse_q.numpy()
+            out[f"{name}.fine_to_row"] = qp.fine_to_local_coarse_row.numpy().astype(np.int32)
         mm = min(m, layout.source_len)
         lists = torch.stack([torch.stack([torch.randperm(layout.source_len, generator=g)[:mm] for _ in range(nq)]) for _ in range(2)])
         fine = attn._expand_source_downsample_chunk(lists, layout, state, topk, n)

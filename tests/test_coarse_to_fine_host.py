@@ -18,6 +18,8 @@ def test_source_table_and_budget_match_the_reference(name):
     assert np.array_equal(lay.table.numpy(), g["table"])
     assert [lay.source_len, lay.special_count, lay.edge_count, lay.coarse_count] == g["counts"][:4].tolist()
     assert lay.kept_sources(topk) == int(g["counts"][4])
+    if "fine_to_row" in g:
+        assert np.array_equal(lay.token_source.numpy(), g["fine_to_row"])
     assert source_layout(tpv, views, special, gh, gw, "cpu") is lay  # cached
 
 

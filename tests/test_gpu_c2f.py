@@ -132,3 +132,40 @@ def test_layer_with_pooled_sources_eager_and_graph():
     ref_out, _, _ = orc.sparse_attention(q.cpu()[:, rows], kk.cpu(), v.cpu(), idx_g[:, rows.to(dev())].cpu(), 0.125)
     got = out_g.view(1, N, heads, 64)[:, rows.to(dev())].float().cpu()
     assert (got - ref_out).abs().max().item() <= 2e-2
+
+
+def test_pooled_queries_take_their_cells_list():
+    """qk_sym_x2_broadcast: queries pooled like the keys (checked against the reference's pooled queries), one list per
+    source, every token takes its source's list."""
+    name = "vggt1"
+    tpv, views, special, gh, gw, _, _, _ = CASES[name]
+    lay = source_layout(tpv, views, special, gh, gw, dev())
+    olay = orc.source_layout(tpv, views, special, gh, gw)
+    g = GOLD[name]
+    k = torch.from_numpy(g["k"]).to(dev())
+    cq, none = pool_sources(k, None, lay)
+    assert none is None and np.allclose(cq.cpu().numpy(), g["coarse_q"], rtol=0, atol=1e-6)
+    assert np.array_equal(lay.token_source.cpu().numpy(), g["fine_to_row"])
+    N, topk = tpv * views, 128
+    gen = torch.Generator().manual_seed(3)
+    q = torch.randn(1, N, 4, 64, generator=gen).bfloat16().to(dev())
+    kk = torch.randn(1, N, 4, 64, generator=gen).bfloat16().to(dev())
+    w = torch.rand(1, N, 4, generator=gen).bfloat16().to(dev())
+    idx = select_topk_coarse_to_fine(q, kk, w, lay, topk, 0.125, pool_queries=True)
+    geoweave_b200.check_status()
+    assert tuple(idx.shape) == (1, N, topk) and idx.dtype == torch.int32
+    # one list per source, from the pooled queries scored against the pooled keys
+    sq, _ = pool_sources(q, None, lay)
+    sk, sw = pool_sources(kk, w, lay)
+    lists = select_topk_coarse_to_fine(sq, kk, w, lay, topk, 0.125)          # pooled queries as an ordinary query block
+    assert torch.equal(idx, lists.index_select(1, lay.token_source))
+    src = orc.token_source(olay)
+    assert torch.equal(idx.cpu()[0, 7], lists.cpu()[0, src[7]])
+    # and those lists against the oracle's scores of the oracle's pooled queries
+    oq, _ = orc.pool_sources(q.cpu(), w.cpu(), olay)
+    assert torch.equal(sq.cpu(), oq.bfloat16())
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import fused_score_topk
+    m = lay.kept_sources(topk)
+    kept, _ = fused_score_topk(sq, sk, sw, m, 0.125, return_scores=True)
+    res = orc.audit_topk(kept.cpu(), orc.indexer_scores(sq.cpu(), sk.cpu(), sw.cpu(), 0.125), m, sq.cpu(), sk.cpu(), sw.cpu(), 0.125)
+    assert res["out_of_range"] == 0 and res["duplicates"] == 0 and res["unexplained"] == 0, res

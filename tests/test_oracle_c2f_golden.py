@@ -30,6 +30,9 @@ def test_pooled_sources(name):
     ks, ws = orc.pool_sources(torch.from_numpy(g["k"]), torch.from_numpy(g["w"]), lay)
     assert np.allclose(ks.numpy(), g["src_k"], rtol=0, atol=1e-6)
     assert np.allclose(ws.numpy(), g["src_w"], rtol=0, atol=1e-6)
+    # pooled queries (the whole sequence as one chunk) are the same means, and every token takes its source's row
+    assert np.allclose(ks.numpy(), g["coarse_q"], rtol=0, atol=1e-6)
+    assert np.array_equal(orc.token_source(lay).numpy(), g["fine_to_row"])
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
