@@ -52,6 +52,8 @@ def parse():
     ap.add_argument("--no-extra-legs", action="store_true",
                     help="skip the legs measured after the main region (attention in the HBM regime, the 256-view context, "
                          "operator inputs from the reference's projections)")
+    ap.add_argument("--attn-bwd", action="store_true",
+                    help="run only the attention backward on 8192 query rows of the main workload's shape (for profiler captures)")
     ap.add_argument("--attn-hbm", action="store_true",
                     help="run only the attention kernel in the regime where HBM binds (8192 queries, k = 1024, positions uniformly "
                          "random over 266496 keys: K + V = 1.09 GB) and print one JSON line; small enough for an ncu capture")
@@ -804,10 +806,48 @@ def run_attn_hbm(args):
                       "bytes_per_launch": nbytes, "achieved_gbs": nbytes / ms / 1e6}), flush=True)
 
 
+def run_attn_bwd(args):
+    """The attention backward alone on a block of query rows of the main workload (see --attn-bwd): small enough for a
+    multi-pass profiler capture (K + V = 136 MB, scratch 0.5 GB), large enough that DRAM figures mean something."""
+    import geoweave_b200
+    from geoweave_b200 import _lib
+    from geoweave_b200.custom_flash_attn.sparse_index_flash_attn import sparse_attention_backward, sparse_attention_forward
+
+    _lib.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    S, T, bf = 32 * 1041, 8192, torch.bfloat16
+    gg = torch.Generator(device=dev).manual_seed(77)
+    k = torch.randn(1, S, H, D, device=dev, dtype=bf, generator=gg)
+    v = torch.randn(1, S, H, D, device=dev, dtype=bf, generator=gg)
+    q = torch.randn(1, T, H, D, device=dev, dtype=bf, generator=gg)
+    pos = torch.randint(0, S, (1, T, TOPK), device=dev, dtype=torch.int32, generator=gg)
+    o, _, lse = sparse_attention_forward(q, k, v, pos, None, False, True, "bthd")
+    d_o = torch.randn_like(o)
+    fn = lambda: sparse_attention_backward(q, k, v, pos, o, lse, d_o, None, None)
+    for _ in range(max(1, args.warmup)):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(max(1, args.steps)):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    geoweave_b200.check_status()
+    ms = a.elapsed_time(b) / max(1, args.steps)
+    pairs = T * TOPK
+    print(json.dumps({"leg": "attention backward", "queries": T, "keys": S, "topk": TOPK, "ms_per_call": ms,
+                      "gather_bytes_per_kernel": pairs * 2 * H * D * 2, "scratch_bytes": pairs * H * 4}), flush=True)
+
+
 def main():
     args = parse()
     if args.attn_hbm:
         run_attn_hbm(args)
+        return
+    if args.attn_bwd:
+        run_attn_bwd(args)
         return
     if args.micro:
         run_micro(args)
