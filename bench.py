@@ -49,6 +49,10 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers per step (profiling)")
     ap.add_argument("--profile", action="store_true", help="profiling run: exact --warmup, no e2e pass, no CPU arm")
+    ap.add_argument("--gather", choices=("group", "packed", "peer"), default="peer",
+                    help="N > 1: how K_idx with w, and K with V, reach every rank: pulled from peer memory behind a flag barrier "
+                         "(PeerExchange, default; NCCL packed where peer-mapped memory cannot be set up), one NCCL all-gather of the "
+                         "pair packed side by side, or one coalesced NCCL group into separate tensors")
     ap.add_argument("--no-extra-legs", action="store_true",
                     help="skip the legs measured after the main region (attention in the HBM regime, the 256-view context, "
                          "operator inputs from the reference's projections)")
@@ -223,7 +227,7 @@ def run_ours(args):
     from geoweave_b200 import _lib
     from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_inference_func
     from geoweave_b200.custom_indexer import sparse_topk_indexer_inference_func
-    from geoweave_b200.sharding import gather_rows_group, row_partition
+    from geoweave_b200.sharding import gather_rows_group, gather_rows_packed, row_partition
 
     _lib.load()  # fail loudly if the CUDA library is missing: there is no other path
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -264,24 +268,59 @@ def run_ours(args):
 
     last = {}          # tensors of the most recent recorded layer call (for the bare-gather ceiling)
 
+    use_peer = False
+    if args.gather == "peer" and world > 1:
+        from geoweave_b200.sharding import PeerExchange
+
+        # one object per exchange (each alternates its own buffer halves): K_idx, w by one pull kernel in front of the indexer;
+        # K, V by copy engines beside it.  Where peer-mapped memory cannot be set up, every rank falls back to NCCL.
+        try:
+            ex_idx = PeerExchange(device=dev, pull="kernel")
+            ex_kv = PeerExchange(device=dev, pull="copies", copy_streams=4)
+            ok = torch.ones(1, device=dev)
+        except Exception as exc:
+            ok = torch.zeros(1, device=dev)
+            peer_error = f"{type(exc).__name__}: {exc}"
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        use_peer = bool(ok.item())
+    if use_peer:
+        gather_idx, gather_kv = ex_idx.gather, ex_kv.gather
+        # before anything is timed: three exchanges in a row (both halves of the buffers) must give what NCCL gives
+        for layer in range(3):
+            tt = resident[layer % layers]
+            want = [x.contiguous() for x in gather_rows_packed([tt["k"], tt["v"]], n_tokens).result()]
+            got = ex_kv.gather([tt["k"], tt["v"]], n_tokens, async_op=True).result()
+            want_i = [x.contiguous() for x in gather_rows_packed([tt["k_idx"], tt["w"]], n_tokens).result()]
+            got_i = ex_idx.gather([tt["k_idx"], tt["w"]], n_tokens).result()
+            torch.cuda.synchronize()
+            if not all(torch.equal(a, b) for a, b in zip(want + want_i, got + got_i)):
+                raise RuntimeError("PeerExchange.gather disagrees with the NCCL all-gather")
+        geoweave_b200.check_status()
+    else:
+        gather_idx = gather_kv = gather_rows_group if args.gather == "group" else gather_rows_packed
+
     def layer_op(t, record, n_tok=n_tokens, events=None):
+        if record:
+            eg, e0, e1, ek, e2 = ev(), ev(), ev(), ev(), ev()
+            eg.record()
         if world > 1:  # the indexer needs K_idx and w; K and V are gathered behind it
-            k_idx, w = [x.contiguous() for x in gather_rows_group([t["k_idx"], t["w"]], n_tok).result()]
-            kv_pend = gather_rows_group([t["k"], t["v"]], n_tok, async_op=True)
+            k_idx, w = [x.contiguous() for x in gather_idx([t["k_idx"], t["w"]], n_tok).result()]
+            kv_pend = gather_kv([t["k"], t["v"]], n_tok, async_op=True)
         else:
             k_idx, w, k, v = t["k_idx"], t["w"], t["k"], t["v"]
         if record:
-            e0, e1, e2 = ev(), ev(), ev()
             e0.record()
         idx, _ = sparse_topk_indexer_inference_func(t["q_idx"], k_idx, w, None, TOPK, DI ** -0.5, 0, 0, return_scores=False)
         if record:
             e1.record()
         if world > 1:
             k, v = kv_pend.result()
+        if record:
+            ek.record()
         out, _ = sparse_index_flash_attn_inference_func(t["q"], k, v, idx, None, False, D ** -0.5, False)
         if record:
             e2.record()
-            (stage_events if events is None else events).append((e0, e1, e2))
+            (stage_events if events is None else events).append((e0, e1, e2, eg, ek))
             last.update(idx=idx, k=k, v=v)
         return out
 
@@ -389,8 +428,10 @@ def run_ours(args):
     geoweave_b200.check_status()
     clk = clocks.stop(t_begin, time.perf_counter()) if clocks else None
 
-    idx_ms = statistics.mean(e0.elapsed_time(e1) for e0, e1, _ in stage_events)
-    att_ms = statistics.mean(e1.elapsed_time(e2) for _, e1, e2 in stage_events)
+    idx_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in stage_events)
+    att_ms = statistics.mean(e[4].elapsed_time(e[2]) for e in stage_events)       # the attention launch alone
+    kidx_gather_ms = statistics.mean(e[3].elapsed_time(e[0]) for e in stage_events)  # K_idx and w arriving, in front of the indexer
+    kv_wait_ms = statistics.mean(e[1].elapsed_time(e[4]) for e in stage_events)      # what of the K, V gather the indexer did not cover
     lib = _lib.load()
     launches = layers * (lib.gw_indexer_topk_launch_count(1, rows, n_tokens, TOPK) + 1)
     es = 2
@@ -459,8 +500,10 @@ def run_ours(args):
         t0c = time.perf_counter()
         ms_ctx = timed(lambda: layer_op(tc, True, n_ctx, ctx_events), 2) / 2
         ctx_clk = ctx_clocks.stop(t0c, time.perf_counter()) if ctx_clocks else None
-        ctx = {"ms": ms_ctx, "idx_ms": statistics.mean(a.elapsed_time(b) for a, b, _ in ctx_events),
-               "att_ms": statistics.mean(b.elapsed_time(c) for _, b, c in ctx_events), "rows": chi - clo, "tokens": n_ctx, "clocks": ctx_clk}
+        ctx = {"ms": ms_ctx, "idx_ms": statistics.mean(e[0].elapsed_time(e[1]) for e in ctx_events),
+               "att_ms": statistics.mean(e[4].elapsed_time(e[2]) for e in ctx_events),
+               "kidx_gather_ms": statistics.mean(e[3].elapsed_time(e[0]) for e in ctx_events),
+               "kv_wait_ms": statistics.mean(e[1].elapsed_time(e[4]) for e in ctx_events), "rows": chi - clo, "tokens": n_ctx, "clocks": ctx_clk}
         if world == 1:
             # the selection stage alone, coarse-to-fine (2x2-pooled sources, kept cells expanded) against the full-resolution
             # indexer call, on this context and on the main workload's 32 views
@@ -507,8 +550,8 @@ def run_ours(args):
                 ms_p = timed(lambda: layer_op(tp, True, n_tokens, pev), 3) / 3
                 g_ms = bare_gather_ms(last["k"], last["v"], last["idx"])
                 proj = {"ms_per_layer": ms_p, "tokens_per_s": n_tokens / (ms_p * 1e-3),
-                        "idx_ms": statistics.mean(a.elapsed_time(b) for a, b, _ in pev),
-                        "att_ms": statistics.mean(b.elapsed_time(c) for _, b, c in pev), "bare_gather_ms": g_ms,
+                        "idx_ms": statistics.mean(e[0].elapsed_time(e[1]) for e in pev),
+                        "att_ms": statistics.mean(e[4].elapsed_time(e[2]) for e in pev), "bare_gather_ms": g_ms,
                         "inputs": "q,k,v,q_idx,k_idx,w from the reference's DSABlock projections (qkv + q/k LayerNorm + rotary; "
                                   "LightningIndexer.project) of ~N(0,1) tokens, trunc-normal(0.02) weights, w_proj bias 1"}
                 del tp
@@ -562,6 +605,11 @@ def run_ours(args):
                                      "frac_of_sustained": idx_tfs / tc_sustained, "flops_per_call": idx_flops,
                                      "ms_per_call": idx_ms, "peak_source": peak_src},
                 "clocks": clk}
+        if world > 1:
+            line["exchange"] = {"gather": "peer" if use_peer else ("packed" if args.gather == "peer" else args.gather), "kidx_gather_ms": kidx_gather_ms, "indexer_ms": idx_ms, "kv_wait_ms": kv_wait_ms,
+                                "attention_ms": att_ms, "note": "mean per layer on rank 0's stream (CUDA events): K_idx and w arriving in "
+                                "front of the indexer; the indexer call (the K, V gather runs beside it); what of the K, V gather is "
+                                "left when the indexer ends; the attention launch"}
         if hbm_leg:
             gbs = hbm_leg["bytes"] / (hbm_leg["ms"] * 1e-3) / 1e9
             hbm_traffic = recorded_dram_traffic("sparse_attn_mma_kernel", "attn_hbm", hbm_leg["queries"])
@@ -582,7 +630,8 @@ def run_ours(args):
                 "ms_per_layer": ctx["ms"], "tokens_per_s": ctx["tokens"] / (ctx["ms"] * 1e-3), "indexer_ms": ctx["idx_ms"],
                 "attention_ms": ctx["att_ms"], "indexer_tflops": cf / (ctx["idx_ms"] * 1e-3) / 1e12,
                 "indexer_frac": cf / (ctx["idx_ms"] * 1e-3) / 1e12 / tc_peak,
-                "attention_gbs": attn_bytes_of(ctx["rows"]) / (ctx["att_ms"] * 1e-3) / 1e9, "steps": 2, "warmup": 1, "clocks": ctx["clocks"]}
+                "attention_gbs": attn_bytes_of(ctx["rows"]) / (ctx["att_ms"] * 1e-3) / 1e9,
+                "kidx_gather_ms": ctx["kidx_gather_ms"], "kv_wait_ms": ctx["kv_wait_ms"], "steps": 2, "warmup": 1, "clocks": ctx["clocks"]}
         if ctx and "c2f" in ctx:
             line["coarse_to_fine_selection"] = dict(ctx["c2f"], note="selection stage alone (one call, CUDA events): pooled 2x2 "
                                                     "sources -> fused indexer over the sources -> expansion to 1024 tokens (and, second "

@@ -67,6 +67,12 @@ SIGNATURES = {
     "gw_indexer_topk_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "gw_indexer_topk_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "gw_peer_barrier": (c_int, [c_void_p, c_int, c_int, c_uint, c_int, c_void_p, c_void_p]),
+    "gw_peer_exchange_create": (c_int, [c_int, c_void_p]),
+    "gw_peer_exchange_destroy": (None, [c_void_p]),
+    "gw_peer_exchange_run": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_uint, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_void_p, c_void_p, c_void_p, c_int]),
+    "gw_peer_exchange_join": (c_int, [c_void_p, c_void_p, c_int]),
     "gw_pool_sources": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "gw_expand_sources": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int64, c_int, c_int, c_int, c_void_p,
                                   c_void_p]),

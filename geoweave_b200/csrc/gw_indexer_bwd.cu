@@ -12,10 +12,11 @@
 // of the index lists by key (given by the caller) and sums dk and dw in that fixed order.
 //
 // Both kernels: persistent CTAs, four per SM, of one producer warp and one compute warp per indexer head.  The producer
-// gathers 16 rows per batch with one bulk copy each (k rows of Hi x 64 elements plus the key's w, widened to a 16-byte
-// fp32 line by a small preparation kernel; or q rows plus the pairs' scratch lines) into a ring of four slots; the
+// gathers 16 rows per batch with one bulk copy each (k rows or q rows of Hi x 64 elements) into a ring of four slots; the
 // compute warps run mma.sync m16n8k16 with the vector operand in column 0 of B: z = K_h . q_h from the rows as stored,
-// dq^T += K_h^T . f and dk^T += q_h^T . f from ldmatrix.trans of the same rows.
+// dq^T += K_h^T . f and dk^T += q_h^T . f from ldmatrix.trans of the same rows.  The small per-pair values (the key's w,
+// the pair's scratch entry) are read by the compute warps themselves with plain loads issued one batch ahead: as bulk
+// copies of 16 or 32 bytes they doubled the number of copies, and the copy rate is what bounds these kernels.
 #include "gw_common.cuh"
 
 namespace gw {
@@ -26,7 +27,6 @@ constexpr int IB_BATCH = 16;
 constexpr int IB_NB = 4;
 constexpr int IB_CTAS_PER_SM = 4;
 constexpr int IB_LINE = 32;  // scratch bytes per pair: 4 heads x {f, g relu(z)} fp32
-constexpr int IB_WLINE = 16; // 4 heads x fp32 w
 
 __device__ __forceinline__ void ib_ldmatrix_x4(uint32_t saddr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -70,24 +70,12 @@ struct IbParams {
   const float* g;              // [B,T,K]
   const int32_t* key_order;    // [B,T*K]
   const int32_t* key_start;    // [B,S+1]
-  float* wtab;                 // scratch [B,S,4]
   float2* fr;                  // scratch [B,T,K,4]: {f, g relu(z)}
   void *dq, *dk, *dw;
   int* status;
   int B, T, S, K;
   float scale;
 };
-
-template <typename T, int HI>
-__global__ void ib_prepare_w_kernel(const T* __restrict__ w, float* __restrict__ wtab, long long n) {
-  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-  if (i >= n) return;
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  float* of = reinterpret_cast<float*>(&o);
-#pragma unroll
-  for (int h = 0; h < HI; ++h) of[h] = to_float(w[i * HI + h]);
-  reinterpret_cast<float4*>(wtab)[i] = o;
-}
 
 // a producer that leaves after a timeout lets the copies it started land first (bounded), so that none arrives in
 // shared memory the CTA has already given up
@@ -116,7 +104,7 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_que
   constexpr int ROW = HI * IB_D * 2;
   constexpr int RS = ROW + 16;
   constexpr int ROWS = IB_BATCH * RS;
-  constexpr int SLOT = ROWS + IB_BATCH * IB_WLINE;
+  constexpr int SLOT = ROWS;
   extern __shared__ __align__(128) unsigned char ib_smem[];
   IbShared* sh = reinterpret_cast<IbShared*>(ib_smem + IB_NB * SLOT);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -126,9 +114,9 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_que
   ib_init_barriers<HI>(sh);
 
   if (warp == HI) {
-    // producer: lanes 0..15 fetch the k rows of a batch's keys, lanes 16..31 the keys' w lines
+    // producer: lanes 0..15 fetch the k rows of a batch's keys
     const uint32_t S = static_cast<uint32_t>(p.S);
-    const int key = lane & 15, what = lane >> 4;
+    const int key = lane & 15;
     uint32_t it = 0;
     for (long long qi = blockIdx.x; qi < nq; qi += gridDim.x) {
       const long long b = qi / p.T;
@@ -148,15 +136,12 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_que
         }
         if (lane == 0) {
           sh->mask[slot] = mask;
-          mbar_arrive_expect_tx(&sh->full[slot], IB_BATCH * (ROW + IB_WLINE));
+          mbar_arrive_expect_tx(&sh->full[slot], IB_BATCH * ROW);
         }
         __syncwarp();
         const long long src = b * p.S + (valid ? id : 0);  // a padding entry gathers key 0 and weighs nothing below
-        if (what == 0)
+        if (lane < IB_BATCH)
           bulk_g2s(ib_smem + slot * SLOT + key * RS, static_cast<const unsigned char*>(p.k) + src * ROW, ROW, &sh->full[slot]);
-        else
-          bulk_g2s(ib_smem + slot * SLOT + ROWS + key * IB_WLINE, reinterpret_cast<const unsigned char*>(p.wtab) + src * IB_WLINE,
-                   IB_WLINE, &sh->full[slot]);
       }
     }
     return;
@@ -184,12 +169,28 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_que
 #pragma unroll
       for (int r = 0; r < 4; ++r) acc[db][r] = 0.f;
     const float* gq = p.g + qi * K;
+    const int32_t* iq = p.idx + qi * K;
+    const T* wb = static_cast<const T*>(p.w) + (qi / p.T) * p.S * HI + h;
     float2* frq = p.fr + qi * K * 4;
+    // this lane's two keys of a batch (g8 and g8 + 8): index two batches ahead, weight and gradient one batch ahead
+    const uint32_t S = static_cast<uint32_t>(p.S);
+    auto load_id = [&](int j) { return j < K ? iq[j] : -1; };
+    auto load_w = [&](int id) { return static_cast<uint32_t>(id) < S ? to_float(wb[static_cast<long long>(id) * HI]) : 0.f; };
+    int id0n = load_id(g8), id1n = load_id(g8 + 8);
+    int id0nn = load_id(g8 + IB_BATCH), id1nn = load_id(g8 + 8 + IB_BATCH);
     float g0n = (g8 < K) ? gq[g8] : 0.f, g1n = (g8 + 8 < K) ? gq[g8 + 8] : 0.f;
+    float w0n = load_w(id0n), w1n = load_w(id1n);
 
     for (int bt = 0; bt < nbatch; ++bt, ++it) {
       const int j0 = bt * IB_BATCH + g8, j1 = j0 + 8;
-      const float g0 = g0n, g1 = g1n;
+      const float g0 = g0n, g1 = g1n, w0 = w0n, w1 = w1n;
+      const bool ok0 = static_cast<uint32_t>(id0n) < S, ok1 = static_cast<uint32_t>(id1n) < S;
+      id0n = id0nn;
+      id1n = id1nn;
+      id0nn = load_id(j0 + 2 * IB_BATCH);
+      id1nn = load_id(j1 + 2 * IB_BATCH);
+      w0n = load_w(id0n);
+      w1n = load_w(id1n);
       g0n = (j0 + IB_BATCH < K) ? gq[j0 + IB_BATCH] : 0.f;
       g1n = (j1 + IB_BATCH < K) ? gq[j1 + IB_BATCH] : 0.f;
       const uint32_t slot = it % IB_NB;
@@ -197,10 +198,7 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_que
         report_status(p.status, GW_ERR_TIMEOUT);
         return;
       }
-      const uint32_t mask = sh->mask[slot];
       const uint32_t kbase = smem_base + slot * SLOT;
-      const float* wt = reinterpret_cast<const float*>(ib_smem + slot * SLOT + ROWS);
-      const bool ok0 = (mask >> g8) & 1u, ok1 = (mask >> (g8 + 8)) & 1u;  // keys g8 and g8+8 of the batch
       float z[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
@@ -210,7 +208,6 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_que
       }
       // column 0 lives in the lanes with t4 == 0: element 0 = key g8, element 2 = key g8 + 8
       const float z0 = z[0] * p.scale, z1 = z[2] * p.scale;
-      const float w0 = wt[g8 * 4 + h], w1 = wt[(g8 + 8) * 4 + h];
       const bool on0 = ok0 && z0 > 0.f, on1 = ok1 && z1 > 0.f;
       const float f0 = on0 ? g0 * w0 * p.scale : 0.f, f1 = on1 ? g1 * w1 * p.scale : 0.f;
       const float r0 = on0 ? g0 * z0 : 0.f, r1 = on1 ? g1 * z1 : 0.f;
@@ -254,7 +251,7 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_key
   constexpr int ROW = HI * IB_D * 2;
   constexpr int RS = ROW + 16;
   constexpr int ROWS = IB_BATCH * RS;
-  constexpr int SLOT = ROWS + IB_BATCH * IB_LINE;
+  constexpr int SLOT = ROWS;
   extern __shared__ __align__(128) unsigned char ib_smem[];
   IbShared* sh = reinterpret_cast<IbShared*>(ib_smem + IB_NB * SLOT);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -264,8 +261,8 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_key
   ib_init_barriers<HI>(sh);
 
   if (warp == HI) {
-    // producer: lanes 0..15 fetch the q rows of a batch's pairs, lanes 16..31 the pairs' scratch lines
-    const int ent = lane & 15, what = lane >> 4;
+    // producer: lanes 0..15 fetch the q rows of a batch's pairs
+    const int ent = lane & 15;
     uint32_t it = 0;
     for (long long ki = blockIdx.x; ki < nkeys; ki += gridDim.x) {
       const long long b = ki / p.S, s = ki % p.S;
@@ -287,14 +284,11 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_key
           report_status(p.status, GW_ERR_TIMEOUT);
           return;
         }
-        if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], IB_BATCH * (ROW + IB_LINE));
+        if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], IB_BATCH * ROW);
         __syncwarp();
-        if (what == 0)
+        if (lane < IB_BATCH)
           bulk_g2s(ib_smem + slot * SLOT + ent * RS, static_cast<const unsigned char*>(p.q) + (b * p.T + tq) * ROW, ROW,
                    &sh->full[slot]);
-        else
-          bulk_g2s(ib_smem + slot * SLOT + ROWS + ent * IB_LINE, reinterpret_cast<const unsigned char*>(p.fr) + (b * TK + f) * IB_LINE,
-                   IB_LINE, &sh->full[slot]);
       }
     }
     return;
@@ -317,27 +311,34 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_key
 #pragma unroll
       for (int r = 0; r < 4; ++r) acc[db][r] = 0.f;
     float dw_part = 0.f;
+    // lane l < 16 owns pair l of a batch: its position two batches ahead, its scratch entry {f, g relu(z)} one batch ahead
+    const int32_t* order = p.key_order + b * TK + e0;
+    const float2* frb = p.fr + b * TK * 4 + h;
+    const int pl = lane & 15;
+    auto load_f = [&](int e) { return e < n ? order[e] : -1; };
+    auto load_fr = [&](int f) { return f >= 0 ? frb[static_cast<long long>(f) * 4] : make_float2(0.f, 0.f); };
+    int fn = load_f(pl), fnn = load_f(pl + IB_BATCH);
+    float2 frn = load_fr(fn);
 
     for (int bt = 0; bt < nb; ++bt, ++it) {
+      const float2 fr = frn;   // zero for a pair past the end of the list
+      fn = fnn;
+      fnn = load_f((bt + 2) * IB_BATCH + pl);
+      frn = load_fr(fn);
       const uint32_t slot = it % IB_NB;
       if (!mbar_wait_bounded(&sh->full[slot], (it / IB_NB) & 1u)) {
         report_status(p.status, GW_ERR_TIMEOUT);
         return;
       }
-      const int left = n - bt * IB_BATCH;  // pairs of this batch that exist
       const uint32_t qbase = smem_base + slot * SLOT;
-      const float2* fr = reinterpret_cast<const float2*>(ib_smem + slot * SLOT + ROWS);
-      if (lane < IB_BATCH && lane < left) dw_part += fr[lane * 4 + h].y;
-      uint32_t fb0 = 0u, fb1 = 0u;
-      if (lane < 4) {
-        const int r0 = 2 * t4, r1 = r0 + 1, r2 = r0 + 8, r3 = r0 + 9;
-        const float fa = r0 < left ? fr[r0 * 4 + h].x : 0.f;
-        const float fb = r1 < left ? fr[r1 * 4 + h].x : 0.f;
-        const float fc = r2 < left ? fr[r2 * 4 + h].x : 0.f;
-        const float fd = r3 < left ? fr[r3 * 4 + h].x : 0.f;
-        fb0 = ib_pack2<T>(fa, fb);
-        fb1 = ib_pack2<T>(fc, fd);
-      }
+      if (lane < IB_BATCH) dw_part += fr.y;
+      // B fragment of f: lanes 0..3 need pairs 2t,2t+1 (word 0) and 2t+8,2t+9 (word 1); pair l sits in lane l
+      const float fa = __shfl_sync(0xffffffffu, fr.x, 2 * t4);
+      const float fb = __shfl_sync(0xffffffffu, fr.x, 2 * t4 + 1);
+      const float fc = __shfl_sync(0xffffffffu, fr.x, 2 * t4 + 8);
+      const float fd = __shfl_sync(0xffffffffu, fr.x, 2 * t4 + 9);
+      const uint32_t fb0 = (lane < 4) ? ib_pack2<T>(fa, fb) : 0u;
+      const uint32_t fb1 = (lane < 4) ? ib_pack2<T>(fc, fd) : 0u;
 #pragma unroll
       for (int db = 0; db < 4; ++db) {
         uint32_t a[4];
@@ -365,8 +366,8 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_key
 template <typename T, int HI>
 int launch_indexer_bwd(const IbParams& p, cudaStream_t st) {
   constexpr size_t ROWS = static_cast<size_t>(IB_BATCH) * (HI * IB_D * 2 + 16);
-  constexpr size_t SMEM_Q = IB_NB * (ROWS + IB_BATCH * IB_WLINE) + sizeof(IbShared);
-  constexpr size_t SMEM_K = IB_NB * (ROWS + IB_BATCH * IB_LINE) + sizeof(IbShared);
+  constexpr size_t SMEM_Q = IB_NB * ROWS + sizeof(IbShared);
+  constexpr size_t SMEM_K = IB_NB * ROWS + sizeof(IbShared);
   int dev = 0;
   DeviceFacts facts;
   int rc = device_facts(&dev, &facts);
@@ -378,8 +379,6 @@ int launch_indexer_bwd(const IbParams& p, cudaStream_t st) {
   if (rc != GW_OK) return rc;
   const long long nk = static_cast<long long>(p.B) * p.S, nq = static_cast<long long>(p.B) * p.T;
   const long long cap = static_cast<long long>(facts.sms) * IB_CTAS_PER_SM;
-  ib_prepare_w_kernel<T, HI><<<static_cast<unsigned>((nk + 255) / 256), 256, 0, st>>>(static_cast<const T*>(p.w), p.wtab, nk);
-  GW_LAUNCH_CHECK();
   indexer_bwd_query_kernel<T, HI><<<static_cast<int>(nq < cap ? nq : cap), (HI + 1) * 32, SMEM_Q, st>>>(p);
   GW_LAUNCH_CHECK();
   indexer_bwd_key_kernel<T, HI><<<static_cast<int>(nk < cap ? nk : cap), (HI + 1) * 32, SMEM_K, st>>>(p);
@@ -405,7 +404,8 @@ using namespace gw;
 
 extern "C" size_t gw_indexer_topk_bwd_workspace_bytes(int B, int T, int S, int K) {
   if (B <= 0 || T <= 0 || S <= 0 || K <= 0) return 0;
-  return round_up(static_cast<size_t>(B) * T * K * IB_LINE, 256) + round_up(static_cast<size_t>(B) * S * IB_WLINE, 256);
+  (void)S;
+  return round_up(static_cast<size_t>(B) * T * K * IB_LINE, 256);
 }
 
 extern "C" int gw_indexer_topk_bwd(const void* q, const void* k, const void* w, const int32_t* topk_idx, const float* grad_scores,
@@ -427,7 +427,6 @@ extern "C" int gw_indexer_topk_bwd(const void* q, const void* k, const void* w, 
   IbParams p;
   p.q = q; p.k = k; p.w = w; p.idx = topk_idx; p.g = grad_scores; p.key_order = key_order; p.key_start = key_start;
   p.fr = reinterpret_cast<float2*>(ws);
-  p.wtab = reinterpret_cast<float*>(ws + round_up(static_cast<size_t>(B) * T * K * IB_LINE, 256));
   p.dq = dq; p.dk = dk; p.dw = dw; p.status = status_dev; p.B = B; p.T = T; p.S = S; p.K = K; p.scale = scale;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   return dtype == GW_BF16 ? dispatch_heads<__nv_bfloat16>(p, Hi, st) : dispatch_heads<__half>(p, Hi, st);

@@ -200,6 +200,36 @@ int gw_indexer_topk_bwd(const void* q, const void* k, const void* w, const int32
                         int* status_dev, gw_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * The exchange step of the sharded path over peer memory (GPUs of one node, one process per GPU), in place of an NCCL
+ * all-gather.  Every rank's shard lies in a buffer that all ranks have mapped; one exchange = copy my rows into my
+ * buffer (pack), meet the other ranks at a barrier made of flags in peer memory, pull every peer's rows (pull).
+ *
+ * gw_peer_barrier: flag_ptrs_dev = device array of `world` pointers, entry r = rank r's flag array (uint32 [world], zero
+ * before the first use, mapped by every rank); seq = 1, 2, 3, ... the same on every rank for the same barrier.  One
+ * block; every wait is bounded by limit_ms and reports GW_ERR_TIMEOUT in status_dev.  Only with one process per GPU: ranks
+ * that share a GPU would wait on kernels that cannot run beside them.
+ *
+ * gw_peer_exchange_create/destroy: an object that owns n_copy_streams streams (<= 8) and the events between them, on the
+ * current device.  gw_peer_exchange_run enqueues, behind everything already enqueued on `after`: the n_pack pack copies,
+ * the barrier, and the n_pull (<= 64) pulls -- as device-to-device copies dealt round-robin to the object's streams (copy
+ * engines; no SM used) or, with pull_with_kernel != 0, as one kernel on its first stream.  All pointer arrays are host
+ * arrays of device addresses.  gw_peer_exchange_join makes `waiter` wait for the last run; call it before the next run of
+ * the same object.  Nothing synchronises the host.
+ * No reference counterpart (its multi-GPU form of this path is NCCL all-gathers around the same operators,
+ * easyvolcap/official_vggt/layers/dsa_attention.py:1138-1264).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct GwPeerExchange GwPeerExchange;
+int gw_peer_barrier(const void* flag_ptrs_dev, int rank, int world, unsigned int seq, int limit_ms, int* status_dev,
+                    gw_stream_t stream);
+int gw_peer_exchange_create(int n_copy_streams, GwPeerExchange** out);
+void gw_peer_exchange_destroy(GwPeerExchange* ex);
+int gw_peer_exchange_run(GwPeerExchange* ex, gw_stream_t after, const void* flag_ptrs_dev, int rank, int world, unsigned int seq,
+                         int limit_ms, int* status_dev, int n_pack, const void* const* pack_src, void* const* pack_dst,
+                         const size_t* pack_bytes, int n_pull, const void* const* pull_src, void* const* pull_dst,
+                         const size_t* pull_bytes, int pull_with_kernel);
+int gw_peer_exchange_join(GwPeerExchange* ex, gw_stream_t waiter, int last_was_kernel);
+
+/* ------------------------------------------------------------------------------------------------
  * Coarse-to-fine selection around the indexer (factor-2 pooled sources, round-robin expansion).
  * source_to_fine int32 [L, width] (width <= 4): the tokens of every source, -1 for a missing slot, slots filled from the
  * front.  gw_pool_sources: src_k [B,L,Hi,Di], src_w [B,L,Hi] = mean over a source's tokens of k [B,N,Hi,Di], w [B,N,Hi]
