@@ -493,17 +493,20 @@ def run_ours(args):
         tc = {"q_idx": mk(1, chi - clo, HI, DI), "k_idx": mk(1, chi - clo, HI, DI),
               "w": torch.rand(1, chi - clo, HI, device=dev, generator=gg).to(bf), "q": mk(1, chi - clo, H, D),
               "k": mk(1, chi - clo, H, D), "v": mk(1, chi - clo, H, D)}
-        layer_op(tc, False, n_ctx)
+        ms_warm = timed(lambda: layer_op(tc, False, n_ctx), 1)
         geoweave_b200.check_status()
+        # enough steps for the clock sampler (one sample per 200 ms) to see the region: at least 2, about 0.7 s, at most 32
+        ctx_steps = int(min(32, max(2, -(-700.0 // max(ms_warm, 1.0)))))
         ctx_events = []
         ctx_clocks = Clocks(local) if rank == 0 else None
         t0c = time.perf_counter()
-        ms_ctx = timed(lambda: layer_op(tc, True, n_ctx, ctx_events), 2) / 2
+        ms_ctx = timed(lambda: layer_op(tc, True, n_ctx, ctx_events), ctx_steps) / ctx_steps
         ctx_clk = ctx_clocks.stop(t0c, time.perf_counter()) if ctx_clocks else None
         ctx = {"ms": ms_ctx, "idx_ms": statistics.mean(e[0].elapsed_time(e[1]) for e in ctx_events),
                "att_ms": statistics.mean(e[4].elapsed_time(e[2]) for e in ctx_events),
                "kidx_gather_ms": statistics.mean(e[3].elapsed_time(e[0]) for e in ctx_events),
-               "kv_wait_ms": statistics.mean(e[1].elapsed_time(e[4]) for e in ctx_events), "rows": chi - clo, "tokens": n_ctx, "clocks": ctx_clk}
+               "kv_wait_ms": statistics.mean(e[1].elapsed_time(e[4]) for e in ctx_events), "rows": chi - clo, "tokens": n_ctx, "clocks": ctx_clk,
+               "steps": ctx_steps}
         if world == 1:
             # the selection stage alone, coarse-to-fine (2x2-pooled sources, kept cells expanded) against the full-resolution
             # indexer call, on this context and on the main workload's 32 views
@@ -631,7 +634,7 @@ def run_ours(args):
                 "attention_ms": ctx["att_ms"], "indexer_tflops": cf / (ctx["idx_ms"] * 1e-3) / 1e12,
                 "indexer_frac": cf / (ctx["idx_ms"] * 1e-3) / 1e12 / tc_peak,
                 "attention_gbs": attn_bytes_of(ctx["rows"]) / (ctx["att_ms"] * 1e-3) / 1e9,
-                "kidx_gather_ms": ctx["kidx_gather_ms"], "kv_wait_ms": ctx["kv_wait_ms"], "steps": 2, "warmup": 1, "clocks": ctx["clocks"]}
+                "kidx_gather_ms": ctx["kidx_gather_ms"], "kv_wait_ms": ctx["kv_wait_ms"], "steps": ctx["steps"], "warmup": 1, "clocks": ctx["clocks"]}
         if ctx and "c2f" in ctx:
             line["coarse_to_fine_selection"] = dict(ctx["c2f"], note="selection stage alone (one call, CUDA events): pooled 2x2 "
                                                     "sources -> fused indexer over the sources -> expansion to 1024 tokens (and, second "
