@@ -46,3 +46,37 @@ def test_exchange_of_one_rank_returns_the_rows(one_rank_group, pull):
     geoweave_b200.check_status()
     with pytest.raises(ValueError):
         ex.gather([k_idx[:, :10]], rows)
+
+
+def test_barrier_wait_runs_out_when_a_peer_never_signals():
+    """Two flag arrays on this GPU stand for two ranks; nobody plays rank 1, so rank 0's wait for it must end after the
+    given limit with GW_ERR_TIMEOUT in the status word -- and the context stays usable."""
+    import time
+
+    from geoweave_b200 import _lib
+
+    lib = _lib.load()
+    flags = torch.zeros(2, 64, dtype=torch.int32, device=dev())
+    ptrs = torch.tensor([flags[0].data_ptr(), flags[1].data_ptr()], dtype=torch.int64, device=dev())
+    status = _lib.status_word(dev())
+    status.zero_()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    with torch.cuda.device(dev()):
+        rc = lib.gw_peer_barrier(ptrs.data_ptr(), 0, 2, 1, 20, status.data_ptr(), _lib.stream_ptr(dev()))
+    assert rc == 0
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 0.015 <= waited < 1.0, waited
+    assert int(status.item()) == _lib.GW_ERR_TIMEOUT
+    assert flags[0, 0].item() == 1 and flags[1, 0].item() == 1 and flags[0, 1].item() == 0  # rank 0 signalled both, rank 1 never did
+    with pytest.raises(_lib.GeoWeaveError):
+        geoweave_b200.check_status()
+    status.zero_()
+    # a barrier whose peers have all arrived (the flags are already there) passes at once
+    flags[0, 1] = 1
+    with torch.cuda.device(dev()):
+        assert lib.gw_peer_barrier(ptrs.data_ptr(), 0, 2, 1, 20, status.data_ptr(), _lib.stream_ptr(dev())) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    geoweave_b200.check_status()
