@@ -268,7 +268,7 @@ def run_ours(args):
 
     last = {}          # tensors of the most recent recorded layer call (for the bare-gather ceiling)
 
-    use_peer = False
+    use_peer, peer_error = False, None
     if args.gather == "peer" and world > 1:
         from geoweave_b200.sharding import PeerExchange
 
@@ -283,6 +283,8 @@ def run_ours(args):
             peer_error = f"{type(exc).__name__}: {exc}"
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         use_peer = bool(ok.item())
+        if not use_peer and peer_error is None:
+            peer_error = "another rank could not set up peer-mapped memory"
     if use_peer:
         gather_idx, gather_kv = ex_idx.gather, ex_kv.gather
         # before anything is timed: three exchanges in a row (both halves of the buffers) must give what NCCL gives
@@ -610,7 +612,7 @@ def run_ours(args):
                 "clocks": clk}
         if world > 1:
             line["exchange"] = {"gather": "peer" if use_peer else ("packed" if args.gather == "peer" else args.gather), "kidx_gather_ms": kidx_gather_ms, "indexer_ms": idx_ms, "kv_wait_ms": kv_wait_ms,
-                                "attention_ms": att_ms, "note": "mean per layer on rank 0's stream (CUDA events): K_idx and w arriving in "
+                                "attention_ms": att_ms, "fallback_reason": peer_error, "note": "mean per layer on rank 0's stream (CUDA events): K_idx and w arriving in "
                                 "front of the indexer; the indexer call (the K, V gather runs beside it); what of the K, V gather is "
                                 "left when the indexer ends; the attention launch"}
         if hbm_leg:
