@@ -756,6 +756,16 @@ def run_micro(args):
         ms = timed(lambda: sparse_attention_forward(q, kk, vv, pos, None, with_sum, with_sum, "bthd"), reps=3)
         out.append({"op": name, "shape": [T, S, TOPK], "ms": ms, "bound": "hbm", "achieved": nbytes / ms / 1e6, "peak": hbm_peak,
                     "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak})
+    # the bare gather of the same lists (bulk copies only) with fewer CTAs than SMs: is the rate a per-SM or a chip-wide limit?
+    lib_ = _lib.load()
+    stw = _lib.status_word(dev)
+    for ctas in (148, 116, 74):
+        fn_g = lambda: _lib.check(lib_.gw_debug_gather_rate_ctas(kk.data_ptr(), vv.data_ptr(), pos.data_ptr(), T, S, TOPK, H * D * 2, H * D * 2,
+                                                                 H * D * 2, ctas, stw.data_ptr(), _lib.stream_ptr(dev)), "gather")
+        ms = timed(fn_g, reps=3)
+        out.append({"op": f"bare gather of K and V rows, {ctas} CTAs (one per SM)", "shape": [T, S, TOPK], "ms": ms, "bound": "hbm",
+                    "achieved": nbytes / ms / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak,
+                    "gbs_per_sm": nbytes / ms / 1e6 / ctas})
     # the backward of the same call (dQ, dK, dV; the index lists sorted by key inside the timed call)
     from geoweave_b200.custom_flash_attn.sparse_index_flash_attn import sparse_attention_backward
     o_f, _, lse_f = sparse_attention_forward(q, kk, vv, pos, None, False, True, "bthd")

@@ -85,8 +85,18 @@ gather_rate_kernel(const unsigned char* __restrict__ kbase, const unsigned char*
 }  // namespace
 }  // namespace gw
 
+extern "C" int gw_debug_gather_rate_ctas(const void* k, const void* v, const int32_t* kv_pos, int64_t T, int S, int K, int row_bytes,
+                                         int64_t k_row_stride_bytes, int64_t v_row_stride_bytes, int max_ctas, int* status_dev,
+                                         gw_stream_t stream);
+
 extern "C" int gw_debug_gather_rate(const void* k, const void* v, const int32_t* kv_pos, int64_t T, int S, int K, int row_bytes,
                                     int64_t k_row_stride_bytes, int64_t v_row_stride_bytes, int* status_dev, gw_stream_t stream) {
+  return gw_debug_gather_rate_ctas(k, v, kv_pos, T, S, K, row_bytes, k_row_stride_bytes, v_row_stride_bytes, 0, status_dev, stream);
+}
+
+extern "C" int gw_debug_gather_rate_ctas(const void* k, const void* v, const int32_t* kv_pos, int64_t T, int S, int K, int row_bytes,
+                                         int64_t k_row_stride_bytes, int64_t v_row_stride_bytes, int max_ctas, int* status_dev,
+                                         gw_stream_t stream) {
   using namespace gw;
   if (!k || !v || !kv_pos || T < 0 || S <= 0 || K <= 0) return GW_ERR_INVALID_ARG;
   if (row_bytes <= 0 || row_bytes > GR_MAX_ROW || row_bytes % 16 != 0) return GW_ERR_INVALID_ARG;
@@ -100,7 +110,8 @@ extern "C" int gw_debug_gather_rate(const void* k, const void* v, const int32_t*
   static OncePerDevice once;
   rc = ensure_dynamic_smem(gather_rate_kernel, smem, once, dev);
   if (rc != GW_OK) return rc;
-  const int grid = static_cast<int>(T < facts.sms ? T : facts.sms);
+  int grid = static_cast<int>(T < facts.sms ? T : facts.sms);
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;  // fewer CTAs than SMs: how the rate depends on the SMs that gather
   gather_rate_kernel<<<grid, GR_WARPS * 32, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned char*>(k), static_cast<const unsigned char*>(v), kv_pos, T, S, K, row_bytes, k_row_stride_bytes,
       v_row_stride_bytes, status_dev);
