@@ -766,6 +766,12 @@ def run_micro(args):
         out.append({"op": f"bare gather of K and V rows, {ctas} CTAs (one per SM)", "shape": [T, S, TOPK], "ms": ms, "bound": "hbm",
                     "achieved": nbytes / ms / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak,
                     "gbs_per_sm": nbytes / ms / 1e6 / ctas})
+        fn_l = lambda: _lib.check(lib_.gw_debug_gather_rate_ldg(kk.data_ptr(), vv.data_ptr(), pos.data_ptr(), T, S, TOPK, ctas,
+                                                                _lib.stream_ptr(dev)), "gather")
+        ms = timed(fn_l, reps=3)
+        out.append({"op": f"bare gather with plain 16-byte loads, {ctas} CTAs", "shape": [T, S, TOPK], "ms": ms, "bound": "hbm",
+                    "achieved": nbytes / ms / 1e6, "peak": hbm_peak, "unit": "GB/s", "frac": nbytes / ms / 1e6 / hbm_peak,
+                    "gbs_per_sm": nbytes / ms / 1e6 / ctas})
     # the backward of the same call (dQ, dK, dV; the index lists sorted by key inside the timed call)
     from geoweave_b200.custom_flash_attn.sparse_index_flash_attn import sparse_attention_backward
     o_f, _, lse_f = sparse_attention_forward(q, kk, vv, pos, None, False, True, "bthd")

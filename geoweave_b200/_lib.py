@@ -40,6 +40,7 @@ SIGNATURES = {
     "gw_debug_bounded_wait_selftest": (c_int, [c_uint, c_void_p, c_void_p, c_void_p]),
     "gw_debug_indexer_profile_enable": (c_int, [c_int]),
     "gw_debug_gather_rate": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_void_p]),
+    "gw_debug_gather_rate_ldg": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "gw_debug_gather_rate_ctas": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p,
                                           c_void_p]),
     "gw_indexer_topk_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),

@@ -297,6 +297,9 @@ int gw_project_fused(const void* x, const void* weight, const void* bias, int dt
  * when K and V fit the L2, HBM otherwise).  Writes nothing to global memory.  No reference counterpart. */
 int gw_debug_gather_rate(const void* k, const void* v, const int32_t* kv_pos, int64_t T, int S, int K, int row_bytes,
                          int64_t k_row_stride_bytes, int64_t v_row_stride_bytes, int* status_dev, gw_stream_t stream);
+/* the same rows (contiguous, 2 KB each) fetched with plain 16-byte loads instead of bulk copies: the rate of the L2 -> SM path */
+int gw_debug_gather_rate_ldg(const void* k, const void* v, const int32_t* kv_pos, int64_t T, int S, int K, int max_ctas,
+                             gw_stream_t stream);
 /* the same with at most max_ctas CTAs (0 = one per SM): how the gather rate depends on the number of SMs that gather */
 int gw_debug_gather_rate_ctas(const void* k, const void* v, const int32_t* kv_pos, int64_t T, int S, int K, int row_bytes,
                               int64_t k_row_stride_bytes, int64_t v_row_stride_bytes, int max_ctas, int* status_dev,
