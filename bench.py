@@ -782,7 +782,12 @@ def run_micro(args):
     out.append({"op": "sparse attention backward (query kernel + key kernel + sort of the lists), bf16", "shape": [T, S, TOPK],
                 "ms": ms, "bound": "hbm", "achieved": nbytes_bwd / ms / 1e6, "peak": hbm_peak, "unit": "GB/s",
                 "frac": nbytes_bwd / ms / 1e6 / hbm_peak})
-    del o_f, lse_f, d_o
+    d_sum = torch.randn(1, T, TOPK, device=dev)
+    ms = timed(lambda: sparse_attention_backward(q, kk, vv, pos, o_f, lse_f, d_o, d_sum, None), reps=3)
+    out.append({"op": "sparse attention backward with a gradient through attn_sum (pre-pass over the K rows first), bf16",
+                "shape": [T, S, TOPK], "ms": ms, "bound": "hbm", "achieved": (nbytes_bwd + T * TOPK * 2 * H * D) / ms / 1e6, "peak": hbm_peak,
+                "unit": "GB/s", "frac": (nbytes_bwd + T * TOPK * 2 * H * D) / ms / 1e6 / hbm_peak})
+    del o_f, lse_f, d_o, d_sum
     # the indexer's backward on the same lists: gradients of the selected scores for q_idx, k_idx and w
     from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_topk_backward
     qi_ = torch.randn(1, T, HI, DI, device=dev).bfloat16()

@@ -9,8 +9,8 @@
 //   ds = p (dp' - delta') scale
 //   dQ[t,h] = sum_j ds K[pos[t,j],h]        dK[s,h] = sum_{(t,j): pos[t,j]=s} ds q[t,h]       dV[s,h] = sum_{...} p dO[t,h]
 //
-// 16-bit inputs with 8 or 16 heads and no gradient through attn_sum take the tensor-core kernels of gw_attn_bwd_mma.cuh;
-// everything else (fp32, other head counts, a gradient through attn_sum) takes the two kernels of this file.
+// 16-bit inputs with 8 or 16 heads take the tensor-core kernels of gw_attn_bwd_mma.cuh; everything else (fp32, other head
+// counts) takes the two kernels of this file.
 //
 // Two kernels.  The query kernel (one CTA per query, one warp per head at a time, one lane per selected key)
 // gathers the key's K and V slices, forms p and dp', writes both to a scratch of the shape [B,T,H,K], and gets dQ
@@ -260,9 +260,10 @@ extern "C" int gw_sparse_attn_bwd(const void* q, const void* k, const void* v, c
   p.delta = reinterpret_cast<float*>(ws + 2 * round_up(n * K * sizeof(float), 256));
   p.dq = dq; p.dk = dk; p.dv = dv; p.B = B; p.T = T; p.S = S; p.H = H; p.K = K; p.scale = scale;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype != GW_F32 && d_attn_sum == nullptr && (H == 8 || H == 16) && status_dev != nullptr) {
+  if (dtype != GW_F32 && (H == 8 || H == 16) && status_dev != nullptr) {
     BwdMmaParams m;
     m.q = q; m.k = k; m.v = v; m.o = out; m.d_out = d_out; m.pos = kv_pos; m.lse = lse;
+    m.d_attn_sum = d_attn_sum; m.delta_extra = p.delta;
     m.key_order = key_order; m.key_start = key_start; m.pds = reinterpret_cast<uint32_t*>(ws);
     m.dq = dq; m.dk = dk; m.dv = dv; m.status = status_dev; m.B = B; m.T = T; m.S = S; m.H = H; m.K = K; m.scale = scale;
     if (dtype == GW_BF16) return H == 16 ? launch_bwd_mma<__nv_bfloat16, 2>(m, st) : launch_bwd_mma<__nv_bfloat16, 1>(m, st);

@@ -1,5 +1,5 @@
-// Backward of the sparse attention, tensor-core form for 16-bit inputs with token-major rows of 8 or 16 heads x 64
-// and no gradient arriving through attn_sum.  (Included by gw_attn_bwd.cu.)
+// Backward of the sparse attention, tensor-core form for 16-bit inputs with token-major rows of 8 or 16 heads x 64.
+// (Included by gw_attn_bwd.cu.)
 //
 // Both kernels are the forward's machine turned to other operands: one persistent CTA per SM, four producer warps that
 // gather whole token rows with one bulk copy each into a ring of three batch slots (16 rows per tensor per batch, rows
@@ -16,6 +16,9 @@
 //     and the pairs' scratch lines)
 //     dK_h^T += q_h^T . ds      dV_h^T += dO_h^T . p                          (A = ldmatrix.trans of the gathered rows)
 //   The pairs of a key come from a stable sort of the index lists by key, so every sum runs in a fixed order.
+//   With a gradient g = d_attn_sum[t,j] arriving through attn_sum (the same for all heads of a pair) dp becomes dp + g and
+//   delta becomes delta + sum_j p g.  That sum needs p before ds can be formed, so a pre-pass of the query kernel (MODE 2:
+//   gathers the K rows only, s and p as above) writes it per (query, head); the main pass (MODE 1) reads it back.
 #pragma once
 
 namespace gw {
@@ -68,6 +71,8 @@ struct BwdMmaParams {
   const void *q, *k, *v, *o, *d_out;   // contiguous [B,T,H,64] / [B,S,H,64]
   const int32_t* pos;                  // [B,T,K]
   const float* lse;                    // [B,H,T]
+  const float* d_attn_sum;             // [B,T,K] or null
+  float* delta_extra;                  // [B,T,H]: sum_j p d_attn_sum (written by MODE 2, read by MODE 1)
   const int32_t* key_order;            // [B,T*K]
   const int32_t* key_start;            // [B,S+1]
   uint32_t* pds;                       // scratch [B,T,K,H]: low half p, high half ds, both of the input type
@@ -98,7 +103,8 @@ __device__ __forceinline__ void bm_init_barriers(BmShared* sh) {
 // ------------------------------------------------------------------------------------------------------------------
 // query kernel: dQ and the {p, ds} scratch
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T, int HPW>
+// MODE 0: dQ and the scratch.  MODE 1: the same with d_attn_sum.  MODE 2: only sum_j p d_attn_sum per (query, head).
+template <typename T, int HPW, int MODE>
 __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_query_mma_kernel(const BwdMmaParams p) {
   constexpr int D = 64;
   constexpr int H = BM_WARPS * HPW;
@@ -139,11 +145,11 @@ __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_query_mma_kernel(const
         }
         if (lane == 0) {
           sh->mask[slot][pw] = mask;
-          mbar_arrive_expect_tx(&sh->full[slot], 2 * BM_KPP * ROW);
+          mbar_arrive_expect_tx(&sh->full[slot], (MODE == 2 ? 1 : 2) * BM_KPP * ROW);
         }
         __syncwarp();
-        // a padding entry gathers key 0 (finite values) and weighs nothing below
-        if (lane < 2 * BM_KPP)
+        // a padding entry gathers key 0 (finite values) and weighs nothing below; the pre-pass needs the K rows only
+        if (lane < (MODE == 2 ? 1 : 2) * BM_KPP)
           bulk_g2s(bm_smem + slot * SLOT + tens * TENS + key * RS, src0 + static_cast<int64_t>(valid ? id : 0) * ROW, ROW,
                    &sh->full[slot]);
       }
@@ -186,8 +192,17 @@ __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_query_mma_kernel(const
       float dl = fmaf(a0, c0, a1 * c1);
 #pragma unroll
       for (int d = 16; d > 0; d >>= 1) dl += __shfl_xor_sync(0xffffffffu, dl, d);
-      delta[i] = dl;
+      delta[i] = MODE == 1 ? dl + p.delta_extra[qi * H + h] : dl;
       lse2[i] = p.lse[(b * H + h) * static_cast<long long>(p.T) + t] * log2e;
+    }
+    float corr[HPW];
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) corr[i] = 0.f;
+    const float* da = MODE != 0 ? p.d_attn_sum + qi * K : nullptr;
+    float da0n = 0.f, da1n = 0.f;  // this lane's two keys of the next batch (g and g + 8)
+    if (MODE != 0) {
+      da0n = g < K ? da[g] : 0.f;
+      da1n = g + 8 < K ? da[g + 8] : 0.f;
     }
     float acc[HPW][4][4];
 #pragma unroll
@@ -210,6 +225,11 @@ __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_query_mma_kernel(const
       const uint32_t kbase = smem_base + slot * SLOT, vbase = kbase + TENS;
       const bool ok0 = (mask >> g) & 1u, ok1 = (mask >> (g + 8)) & 1u;  // keys g and g+8 of the batch
       const int j0 = bt * BM_BATCH + g, j1 = j0 + 8;
+      const float da0 = da0n, da1 = da1n;
+      if (MODE != 0) {
+        da0n = j0 + BM_BATCH < K ? da[j0 + BM_BATCH] : 0.f;
+        da1n = j1 + BM_BATCH < K ? da[j1 + BM_BATCH] : 0.f;
+      }
 #pragma unroll
       for (int i = 0; i < HPW; ++i) {
         const int h = h0 + i;
@@ -219,14 +239,20 @@ __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_query_mma_kernel(const
           uint32_t a[4];
           bm_ldmatrix_x4(kbase + row_lane_off + h * (D * 2) + ks * 32, a);
           bm_mma<T>(s, a, qb[i][ks][0], qb[i][ks][1]);
-          bm_ldmatrix_x4(vbase + row_lane_off + h * (D * 2) + ks * 32, a);
-          bm_mma<T>(dp, a, dob[i][ks][0], dob[i][ks][1]);
+          if (MODE != 2) {
+            bm_ldmatrix_x4(vbase + row_lane_off + h * (D * 2) + ks * 32, a);
+            bm_mma<T>(dp, a, dob[i][ks][0], dob[i][ks][1]);
+          }
         }
         // column 0 lives in the lanes with t4 == 0: element 0 = key g, element 2 = key g + 8
         const float p0 = ok0 ? exp2f(fmaf(s[0], scale_log2, -lse2[i])) : 0.f;
         const float p1 = ok1 ? exp2f(fmaf(s[2], scale_log2, -lse2[i])) : 0.f;
-        const float ds0 = p0 * (dp[0] - delta[i]) * p.scale;
-        const float ds1 = p1 * (dp[2] - delta[i]) * p.scale;
+        if (MODE == 2) {
+          corr[i] = fmaf(p0, da0, fmaf(p1, da1, corr[i]));
+          continue;
+        }
+        const float ds0 = p0 * (dp[0] + da0 - delta[i]) * p.scale;
+        const float ds1 = p1 * (dp[2] + da1 - delta[i]) * p.scale;
         const uint32_t w0 = bm_pack2<T>(p0, ds0), w1 = bm_pack2<T>(p1, ds1);
         if (t4 == 0) {
           if (j0 < K) pds_q[static_cast<long long>(j0) * H + h] = w0;
@@ -250,6 +276,17 @@ __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_query_mma_kernel(const
       if (lane == 0) mbar_arrive(&sh->empty[slot]);
     }
 
+    if (MODE == 2) {
+      // the lanes with t4 == 0 hold the sums of their two keys per batch: add them up over g
+#pragma unroll
+      for (int i = 0; i < HPW; ++i) {
+        float c = t4 == 0 ? corr[i] : 0.f;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
+        if (lane == 0) p.delta_extra[qi * H + h0 + i] = c;
+      }
+      continue;
+    }
     // lanes with t4 == 0 hold dims g and g+8 of every 16-dim block
     if (t4 == 0) {
 #pragma unroll
@@ -400,24 +437,40 @@ __global__ void __launch_bounds__(BM_THREADS, 1) attn_bwd_key_mma_kernel(const B
   }
 }
 
+template <typename T, int HPW, int MODE>
+int launch_bwd_query_mma(const BwdMmaParams& p, int dev, int sms, cudaStream_t st) {
+  constexpr int H = BM_WARPS * HPW;
+  constexpr size_t SMEM_Q = BM_NB * static_cast<size_t>(2) * BM_BATCH * (H * 64 * 2 + 16) + sizeof(BmShared);
+  static OncePerDevice once;
+  int rc = ensure_dynamic_smem(attn_bwd_query_mma_kernel<T, HPW, MODE>, SMEM_Q, once, dev);
+  if (rc != GW_OK) return rc;
+  const long long nq = static_cast<long long>(p.B) * p.T;
+  attn_bwd_query_mma_kernel<T, HPW, MODE><<<static_cast<int>(nq < sms ? nq : sms), BM_THREADS, SMEM_Q, st>>>(p);
+  GW_LAUNCH_CHECK();
+  return GW_OK;
+}
+
 template <typename T, int HPW>
 int launch_bwd_mma(const BwdMmaParams& p, cudaStream_t st) {
   constexpr int H = BM_WARPS * HPW;
   constexpr size_t ROWS = static_cast<size_t>(2) * BM_BATCH * (H * 64 * 2 + 16);
-  constexpr size_t SMEM_Q = BM_NB * ROWS + sizeof(BmShared);
   constexpr size_t SMEM_K = BM_NB * (ROWS + BM_BATCH * H * 4) + sizeof(BmShared);
   int dev = 0;
   DeviceFacts facts;
   int rc = device_facts(&dev, &facts);
   if (rc != GW_OK) return rc;
-  static OncePerDevice once_q, once_k;
-  rc = ensure_dynamic_smem(attn_bwd_query_mma_kernel<T, HPW>, SMEM_Q, once_q, dev);
+  if (p.d_attn_sum != nullptr) {
+    rc = launch_bwd_query_mma<T, HPW, 2>(p, dev, facts.sms, st);
+    if (rc != GW_OK) return rc;
+    rc = launch_bwd_query_mma<T, HPW, 1>(p, dev, facts.sms, st);
+  } else {
+    rc = launch_bwd_query_mma<T, HPW, 0>(p, dev, facts.sms, st);
+  }
   if (rc != GW_OK) return rc;
+  static OncePerDevice once_k;
   rc = ensure_dynamic_smem(attn_bwd_key_mma_kernel<T, HPW>, SMEM_K, once_k, dev);
   if (rc != GW_OK) return rc;
-  const long long nq = static_cast<long long>(p.B) * p.T, nk = static_cast<long long>(p.B) * p.S;
-  attn_bwd_query_mma_kernel<T, HPW><<<static_cast<int>(nq < facts.sms ? nq : facts.sms), BM_THREADS, SMEM_Q, st>>>(p);
-  GW_LAUNCH_CHECK();
+  const long long nk = static_cast<long long>(p.B) * p.S;
   attn_bwd_key_mma_kernel<T, HPW><<<static_cast<int>(nk < facts.sms ? nk : facts.sms), BM_THREADS, SMEM_K, st>>>(p);
   GW_LAUNCH_CHECK();
   return GW_OK;

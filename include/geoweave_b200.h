@@ -171,8 +171,9 @@ int gw_sparse_attn_fwd(const void* q, const void* k, const void* v, const int32_
  * t*K + j of kv_pos (int32 [B, T*K]) stably sorted by key with padding entries last, and the first entry of every key
  * (int32 [B, S+1]) -- so results are reproducible.  workspace: gw_sparse_attn_bwd_workspace_bytes(B,T,H,K) bytes,
  * 256-byte aligned (p and dp per (query, head, slot)).  Requirements: D = 64, H <= 32, T*K < 2^31.  16-bit inputs with
- * 8 or 16 heads, no d_attn_sum and a status word take tensor-core kernels (gathers by bulk copies, bounded waits that
- * report GW_ERR_TIMEOUT in status_dev); every other case takes plain kernels and status_dev may be null.
+ * 8 or 16 heads and a status word take tensor-core kernels (gathers by bulk copies, bounded waits that report
+ * GW_ERR_TIMEOUT in status_dev; with d_attn_sum a pre-pass over the K rows first); every other case takes plain kernels
+ * and status_dev may be null.
  * Replaces: easyvolcap/utils/custom_flash_attn/sparse_index_flash_attn.py:2442-2846 (_sparse_index_flash_attn_backward and
  *           its Triton kernels :535-1186, fp32 atomic adds) and csrc/sparse_bwd_grouped_kernel.cu:78-603 (sort-based).
  * ---------------------------------------------------------------------------------------------- */

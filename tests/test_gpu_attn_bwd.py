@@ -44,10 +44,11 @@ def make(B, T, S, H, K, dtype, seed, pad=True):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-4), (torch.bfloat16, 1e-2), (torch.float16, 1e-2)])
-# 16-bit, 8 or 16 heads, no gradient through attn_sum: the tensor-core kernels; every other row: the plain kernels
+# 16-bit with 8 or 16 heads: the tensor-core kernels (with a gradient through attn_sum: their pre-pass too); fp32 and the
+# other head counts: the plain kernels
 @pytest.mark.parametrize("B,T,S,H,K,with_sum", [(1, 150, 400, 16, 96, False), (2, 90, 250, 8, 33, False), (1, 300, 100, 16, 50, False),
-                                                (1, 40, 3000, 16, 7, False), (1, 150, 400, 16, 96, True), (2, 90, 250, 4, 33, True),
-                                                (1, 64, 64, 2, 64, True)])
+                                                (1, 40, 3000, 16, 7, False), (1, 150, 400, 16, 96, True), (2, 90, 250, 8, 33, True),
+                                                (1, 300, 100, 16, 50, True), (2, 90, 250, 4, 33, True), (1, 64, 64, 2, 64, True)])
 def test_backward_matches_autograd_of_the_plain_formulation(dtype, tol, B, T, S, H, K, with_sum):
     from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_func
 
