@@ -13,9 +13,9 @@ def group_by_key(positions: torch.Tensor, n_keys: int) -> Tuple[torch.Tensor, to
     The sort is stable, so the pairs of a key stay in (query, slot) order and sums taken in this order are reproducible."""
     B, T, K = positions.shape
     dev = positions.device
-    flat = positions.reshape(B, T * K).to(torch.int64)
+    flat = positions.reshape(B, T * K).to(torch.int32)  # 32-bit keys: half the passes of the radix sort
     flat = torch.where((flat < 0) | (flat >= n_keys), torch.full_like(flat, n_keys), flat)
     keys_sorted, order = torch.sort(flat, dim=1, stable=True)
-    bounds = torch.arange(n_keys + 1, device=dev, dtype=torch.int64).unsqueeze(0).expand(B, n_keys + 1).contiguous()
-    start = torch.searchsorted(keys_sorted, bounds).to(torch.int32).contiguous()
+    bounds = torch.arange(n_keys + 1, device=dev, dtype=torch.int32).unsqueeze(0).expand(B, n_keys + 1).contiguous()
+    start = torch.searchsorted(keys_sorted, bounds, out_int32=True).contiguous()
     return order.to(torch.int32).contiguous(), start
