@@ -66,9 +66,25 @@ def _worker(rank, world, port, n_tokens, case, q):
             assert torch.equal(ki, full["k_idx"]) and torch.equal(ww, full["w"])
             assert torch.equal(kk, full["k"]) and torch.equal(vv, full["v"].double()) and vv.dtype == torch.float64
             q.put((rank, "ok"))
-        elif case == "layer":
+        elif case in ("layer", "layer_exchange"):
+            exchange = None
+            if case == "layer_exchange":
+                # stand-ins with the interface of PeerExchange (gather(xs, n_rows, async_op) -> .result()): the layer must
+                # route K_idx with w through the first and K with V, asynchronously, through the second
+                class Stub:
+                    def __init__(self):
+                        self.calls = []
+
+                    def gather(self, xs, n_rows, async_op=False):
+                        self.calls.append((len(xs), async_op))
+                        return gather_rows_group(xs, n_rows, None, async_op)
+
+                exchange = (Stub(), Stub())
             out, idx = sparse_global_attention_sharded(mine["q_idx"], mine["k_idx"], mine["w"], mine["q"], mine["k"],
-                                                       mine["v"], 5, n_tokens, idx_scale=0.5, attn_scale=0.5, ops=_oracle_ops())
+                                                       mine["v"], 5, n_tokens, idx_scale=0.5, attn_scale=0.5, ops=_oracle_ops(),
+                                                       exchange=exchange)
+            if exchange is not None:
+                assert exchange[0].calls == [(2, False)] and exchange[1].calls == [(2, True)]
             q.put((rank, (out, idx)))
         elif case == "bad_shard":
             try:
@@ -104,11 +120,12 @@ def test_gather_rows_roundtrip_even_and_ragged(world, n_tokens):
     assert res == {r: "ok" for r in range(world)}
 
 
-def test_sharded_layer_equals_single_rank_result():
+@pytest.mark.parametrize("case", ["layer", "layer_exchange"])
+def test_sharded_layer_equals_single_rank_result(case):
     from oracle import gw_oracle as orc
 
     world, n_tokens = 2, 13
-    res = _run(world, n_tokens, "layer")
+    res = _run(world, n_tokens, case)
     g = torch.Generator().manual_seed(123)
     q_idx = torch.randint(-3, 4, (1, n_tokens, 2, 8), generator=g).float()
     k_idx = torch.randint(-3, 4, (1, n_tokens, 2, 8), generator=g).float()
