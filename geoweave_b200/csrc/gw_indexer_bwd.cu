@@ -61,7 +61,6 @@ __device__ __forceinline__ uint32_t ib_pack2(float lo, float hi) {
 
 struct IbShared {
   uint64_t full[IB_NB], empty[IB_NB];
-  uint32_t mask[IB_NB];
 };
 
 struct IbParams {
@@ -127,17 +126,13 @@ __global__ void __launch_bounds__((HI + 1) * 32, IB_CTAS_PER_SM) indexer_bwd_que
         const int kn = (bt + 1) * IB_BATCH + key;
         id_next = (bt + 1 < nbatch && kn < K) ? idx[kn] : -1;
         const bool valid = static_cast<uint32_t>(id) < S;
-        const uint32_t mask = __ballot_sync(0xffffffffu, valid) & 0xffffu;
         const uint32_t slot = it % IB_NB;
         if (!mbar_wait_bounded(&sh->empty[slot], ((it / IB_NB) & 1u) ^ 1u)) {
           ib_drain(sh->full, it);
           report_status(p.status, GW_ERR_TIMEOUT);
           return;
         }
-        if (lane == 0) {
-          sh->mask[slot] = mask;
-          mbar_arrive_expect_tx(&sh->full[slot], IB_BATCH * ROW);
-        }
+        if (lane == 0) mbar_arrive_expect_tx(&sh->full[slot], IB_BATCH * ROW);
         __syncwarp();
         const long long src = b * p.S + (valid ? id : 0);  // a padding entry gathers key 0 and weighs nothing below
         if (lane < IB_BATCH)

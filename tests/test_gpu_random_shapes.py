@@ -109,3 +109,53 @@ def test_attention_with_random_padding_matches_torch(seed):
         assert (o.float()[0] - ref).abs().max().item() <= (1e-4 if dt == torch.float32 else 2e-2), cfg
         if want_sum:
             assert (asum[0] - pr.sum(1)).abs().max().item() <= (1e-4 if dt == torch.float32 else 4e-3), cfg
+
+
+@pytest.mark.parametrize("seed", [11, 12])
+def test_both_backward_passes_on_random_shapes_match_autograd(seed):
+    """Random sizes, head counts, dtypes, padding and duplicates in the lists; with and without a gradient through
+    attn_sum: the attention's dQ, dK, dV and the indexer's dq, dk, dw against torch autograd of plain formulations."""
+    import geoweave_b200
+    from geoweave_b200.custom_flash_attn import sparse_index_flash_attn_func
+    from geoweave_b200.custom_indexer.sparse_topk_indexer import indexer_topk_backward
+
+    g = torch.Generator().manual_seed(seed)
+    for _ in range(12):
+        T, S = _ri(g, 1, 300), _ri(g, 2, 2000)
+        K = [_ri(g, 1, 20), _ri(g, 20, 200), _ri(g, 200, 400)][_ri(g, 0, 2)]
+        H = [16, 8, 4, 2][_ri(g, 0, 3)]
+        dt = [torch.bfloat16, torch.float16, torch.float32][_ri(g, 0, 2)]
+        with_sum = bool(_ri(g, 0, 1))
+        q, kk, v = [torch.randn(1, n, H, 64, generator=g).to(dt) for n in (T, S, S)]
+        pos = torch.randint(-S // 5 - 1, S + S // 5 + 1, (1, T, K), generator=g).to(torch.int32)   # padding and duplicates
+        d_o, d_a = torch.randn(1, T, H, 64, generator=g).to(dt), torch.randn(1, T, K, generator=g)
+        cfg = dict(T=T, S=S, K=K, H=H, dtype=str(dt), with_sum=with_sum)
+        qd, kd, vd = [x.to(dev()).requires_grad_() for x in (q, kk, v)]
+        o, a = sparse_index_flash_attn_func(qd, kd, vd, pos.to(dev()), None, False, 0.125)
+        loss = (o.float() * d_o.to(dev()).float()).sum() + ((a * d_a.to(dev())).sum() if with_sum else 0.0)
+        loss.backward()
+        geoweave_b200.check_status()
+        qr, kr, vr = [x.float().to(dev()).requires_grad_() for x in (q, kk, v)]
+        valid = ((pos >= 0) & (pos < S)).to(dev())
+        safe = torch.where(valid, pos.to(dev()), torch.zeros_like(pos.to(dev()))).long()
+        s = torch.einsum("thd,tkhd->thk", qr[0], kr[0][safe[0]]) * 0.125
+        pr = torch.nan_to_num(torch.softmax(s.masked_fill(~valid[0].unsqueeze(1), float("-inf")), -1), nan=0.0)
+        pr = torch.where(valid[0].unsqueeze(1), pr, torch.zeros_like(pr))
+        o_ref = torch.einsum("thk,tkhd->thd", pr, vr[0][safe[0]])
+        ((o_ref * d_o.to(dev()).float()[0]).sum() + ((pr.sum(1) * d_a.to(dev())[0]).sum() if with_sum else 0.0)).backward()
+        tol = 2e-4 if dt == torch.float32 else 1e-2
+        for name, got, ref in (("dq", qd.grad, qr.grad), ("dk", kd.grad, kr.grad), ("dv", vd.grad, vr.grad)):
+            assert (got.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item()), (name, cfg)
+        if dt == torch.float32:
+            continue  # the indexer's backward takes 16-bit operands
+        Hi = _ri(g, 1, 4)
+        qi, ki = [torch.randn(1, n, Hi, 64, generator=g).to(dt) for n in (T, S)]
+        w = torch.randn(1, S, Hi, generator=g).to(dt)
+        got = indexer_topk_backward(qi.to(dev()), ki.to(dev()), w.to(dev()), pos.to(dev()), d_a.to(dev()), 0.125)
+        geoweave_b200.check_status()
+        qr, kr, wr = [x.float().to(dev()).requires_grad_() for x in (qi, ki, w)]
+        z = torch.einsum("thd,tkhd->tkh", qr[0], kr[0][safe[0]]) * 0.125
+        sc = torch.where(valid[0], (wr[0][safe[0]] * torch.relu(z)).sum(-1), torch.zeros_like(z[..., 0]))
+        (sc * d_a.to(dev())[0]).sum().backward()
+        for name, a_, b_ in zip(("dq_idx", "dk_idx", "dw"), got, (qr.grad, kr.grad, wr.grad)):
+            assert (a_.float() - b_).abs().max().item() <= 1e-2 * max(1.0, b_.abs().max().item()), (name, cfg, Hi)
