@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libgeoweave_b200.so")
-SOURCES = ["gw_topk.cu", "gw_attn.cu", "gw_indexer.cu", "gw_frontend.cu", "gw_diag.cu", "gw_indexer_f32.cu", "gw_proj.cu", "gw_attn_bwd.cu", "gw_indexer_bwd.cu", "gw_c2f.cu", "gw_peer.cu"]
+SOURCES = ["gw_topk.cu", "gw_attn.cu", "gw_indexer.cu", "gw_frontend.cu", "gw_diag.cu", "gw_indexer_f32.cu", "gw_proj.cu", "gw_attn_bwd.cu", "gw_indexer_bwd.cu", "gw_c2f.cu", "gw_peer.cu", "gw_lists.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -177,6 +177,14 @@ int gw_sparse_attn_fwd(const void* q, const void* k, const void* v, const int32_
  * Replaces: easyvolcap/utils/custom_flash_attn/sparse_index_flash_attn.py:2442-2846 (_sparse_index_flash_attn_backward and
  *           its Triton kernels :535-1186, fp32 atomic adds) and csrc/sparse_bwd_grouped_kernel.cu:78-603 (sort-based).
  * ---------------------------------------------------------------------------------------------- */
+/* The key_order / key_start arrays both backward passes take: the (query, slot) pairs of kv_pos (int32 [B,T,K]) stably sorted
+ * by key -- key_order int32 [B, T*K] holds t*K + j, padding entries (outside [0,S)) last; key_start int32 [B, S+1] the first
+ * entry of every key.  A radix sort over the bits a key can have.  workspace: gw_group_by_key_workspace_bytes(T,K,S),
+ * 256-byte aligned.  (The reference sorts the same pairs with torch ops in its grouped backward,
+ * easyvolcap/utils/custom_flash_attn/csrc/sparse_bwd_grouped_kernel.cu:78-180 and its Python caller.) */
+size_t gw_group_by_key_workspace_bytes(int T, int K, int S);
+int gw_group_by_key(const int32_t* kv_pos, int B, int T, int K, int S, int32_t* key_order, int32_t* key_start, void* workspace,
+                    size_t workspace_bytes, gw_stream_t stream);
 size_t gw_sparse_attn_bwd_workspace_bytes(int B, int T, int H, int K);
 int gw_sparse_attn_bwd(const void* q, const void* k, const void* v, const int32_t* kv_pos, const void* out, const float* lse,
                        const void* d_out, const float* d_attn_sum, const int32_t* key_order, const int32_t* key_start,

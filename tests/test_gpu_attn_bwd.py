@@ -121,3 +121,15 @@ def test_gradient_through_attn_sum_alone():
     for got, ref in ((qd.grad, qr.grad), (kd.grad, kr.grad)):
         assert (got.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
     assert vd.grad is None or vd.grad.abs().max().item() == 0.0  # attn_sum does not depend on v
+
+
+def test_key_grouping_on_the_device_equals_the_host_form():
+    from geoweave_b200._lists import group_by_key
+
+    g = torch.Generator().manual_seed(4)
+    for B, T, K, S in ((2, 313, 37, 1000), (1, 50, 8, 70000), (1, 1, 1, 1), (1, 2000, 64, 3)):
+        pos = torch.randint(-S // 4 - 1, S + S // 4 + 2, (B, T, K), generator=g, dtype=torch.int32)
+        order_h, start_h = group_by_key(pos, S)
+        order_d, start_d = group_by_key(pos.to(dev()), S)
+        assert order_d.dtype == torch.int32 and start_d.dtype == torch.int32
+        assert torch.equal(order_d.cpu(), order_h) and torch.equal(start_d.cpu(), start_h), (B, T, K, S)
