@@ -123,13 +123,25 @@ def test_gradient_through_attn_sum_alone():
     assert vd.grad is None or vd.grad.abs().max().item() == 0.0  # attn_sum does not depend on v
 
 
-def test_key_grouping_on_the_device_equals_the_host_form():
+def test_key_grouping_is_a_stable_sort_by_key_with_padding_last():
     from geoweave_b200._lists import group_by_key
 
     g = torch.Generator().manual_seed(4)
     for B, T, K, S in ((2, 313, 37, 1000), (1, 50, 8, 70000), (1, 1, 1, 1), (1, 2000, 64, 3)):
         pos = torch.randint(-S // 4 - 1, S + S // 4 + 2, (B, T, K), generator=g, dtype=torch.int32)
-        order_h, start_h = group_by_key(pos, S)
-        order_d, start_d = group_by_key(pos.to(dev()), S)
-        assert order_d.dtype == torch.int32 and start_d.dtype == torch.int32
-        assert torch.equal(order_d.cpu(), order_h) and torch.equal(start_d.cpu(), start_h), (B, T, K, S)
+        order, start = group_by_key(pos.to(dev()), S)
+        assert order.dtype == torch.int32 and start.dtype == torch.int32
+        assert tuple(order.shape) == (B, T * K) and tuple(start.shape) == (B, S + 1)
+        # the same from torch's stable sort on the host
+        flat = pos.reshape(B, T * K).long()
+        flat = torch.where((flat < 0) | (flat >= S), torch.full_like(flat, S), flat)
+        keys_sorted, want = torch.sort(flat, dim=1, stable=True)
+        bounds = torch.arange(S + 1).unsqueeze(0).expand(B, S + 1).contiguous()
+        assert torch.equal(order.cpu().long(), want), (B, T, K, S)
+        assert torch.equal(start.cpu().long(), torch.searchsorted(keys_sorted, bounds)), (B, T, K, S)
+    # pairs of a key in ascending (query, slot) order, empty keys with empty ranges, padding behind the last key
+    pos = torch.tensor([[[5, 5, -1], [2, 5, 9]]], dtype=torch.int32)
+    order, start = group_by_key(pos.to(dev()), 8)
+    assert order.cpu().tolist() == [[3, 0, 1, 4, 2, 5]] and start.cpu().tolist() == [[0, 0, 0, 1, 1, 1, 4, 4, 4]]
+    with pytest.raises(Exception):
+        group_by_key(pos, 8)  # host tensors are refused: there is no CPU path
