@@ -64,3 +64,27 @@ def test_product_package_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 src = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in src.replace("the oracle", ""), f"{f} refers to the oracle"
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 on its own, and a C program that takes the address of an
+    entry point must link against the library."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler here")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "geoweave_b200.h"\n'
+                   "int main(void) { return gw_abi_version() > 0 && gw_strerror(0) != 0 ? 0 : 1; }\n")
+    res = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(root, "include"), "-fsyntax-only", str(src)],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    lib_dir = os.path.join(root, "geoweave_b200")
+    exe = tmp_path / "use_header"
+    res = subprocess.run([gcc, "-std=c99", "-I", os.path.join(root, "include"), str(src), "-o", str(exe), "-L", lib_dir,
+                          "-lgeoweave_b200", f"-Wl,-rpath,{lib_dir}"], capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    assert subprocess.run([str(exe)]).returncode == 0   # metadata calls only: no GPU needed
