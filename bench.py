@@ -440,6 +440,8 @@ def run_ours(args):
     kv_wait_ms = statistics.mean(e[1].elapsed_time(e[4]) for e in stage_events)      # what of the K, V gather the indexer did not cover
     lib = _lib.load()
     launches = layers * (lib.gw_indexer_topk_launch_count(1, rows, n_tokens, TOPK) + 1)
+    if use_peer:
+        launches += layers * 3  # per layer: the two exchanges' barrier kernels and the pull kernel of K_idx, w
     es = 2
 
     def attn_bytes_of(n_rows):
