@@ -217,10 +217,12 @@ __device__ __forceinline__ void fast_reduce_tile(uint32_t taddr, const float* wt
   }
 }
 
-// key tiles [t0, t1) of split `sp`: an even division, so no split is empty while nsplit <= ntiles
-__device__ __forceinline__ void split_range(int sp, int nsplit, int ntiles, int& t0, int& t1) {
-  t0 = static_cast<int>(static_cast<long long>(sp) * ntiles / nsplit);
-  t1 = static_cast<int>(static_cast<long long>(sp + 1) * ntiles / nsplit);
+// key tiles of split `sp`: sp, sp + nsplit, sp + 2 nsplit, ... (`nt` of them; no split is empty while nsplit <= ntiles).
+// Interleaved rather than contiguous ranges: where the high scores of a row crowd into one stretch of the key range
+// (keys of unequal norm laid out in groups, as the pooled sources of the coarse-to-fine selection are), every split
+// still gets its even share of them, and no single list overflows.
+__device__ __forceinline__ void split_tiles(int sp, int nsplit, int ntiles, int& nt) {
+  nt = (ntiles - sp + nsplit - 1) / nsplit;
 }
 
 template <int HI>
@@ -289,12 +291,13 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           break;
         }
         const int rb = blk_begin + item / nsplit, sp = item % nsplit;
-        int t0, t1;
-        split_range(sp, nsplit, ntiles, t0, t1);
+        int nt;
+        split_tiles(sp, nsplit, ntiles, nt);
         mbar_arrive_expect_tx(&sh->q_full, HI * Q_HEAD_BYTES);
 #pragma unroll
         for (int h = 0; h < HI; ++h) tma_load_2d(q_smem + h * Q_HEAD_BYTES, &tmQ, h * DI, rb * BM, &sh->q_full);
-        for (int j = t0; j < t1; ++j, ++tuse) {
+        for (int jl = 0; jl < nt; ++jl, ++tuse) {
+          const int j = sp + jl * nsplit;
           const uint32_t s = tuse % FNSTG, n = tuse / FNSTG;
           const uint32_t ws = tuse % WSLOTS, wn = tuse / WSLOTS;
           pc.start();
@@ -344,9 +347,8 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         pc.stop(0);
         const int item = sh->item[nblk & 1u];
         if (item < 0 || sh->abort_flag) break;
-        int t0, t1;
-        split_range(item % nsplit, nsplit, ntiles, t0, t1);
-        const int nt = t1 - t0;
+        int nt;
+        split_tiles(item % nsplit, nsplit, ntiles, nt);
         for (int j = b; j < nt; j += 2, ++use) {
           const uint32_t tuse = tbase + j;
           pc.start();
@@ -397,9 +399,8 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int item = __shfl_sync(0xffffffffu, sh->item[nblk & 1u], 0);
       if (item < 0 || __shfl_sync(0xffffffffu, sh->abort_flag, 0)) break;
       const int rb = blk_begin + item / nsplit, sp = item % nsplit;
-      int t0, t1;
-      split_range(sp, nsplit, ntiles, t0, t1);
-      const int nt = t1 - t0;
+      int nt;
+      split_tiles(sp, nsplit, ntiles, nt);
       const int row = rb * BM + row_in_tile;
       const bool active = row < p.T;
       const float tau = active ? p.tau_in[row] : INFINITY;
@@ -415,7 +416,7 @@ indexer_fast_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const float tau_eff = wraps ? INFINITY : tau;
       if (wraps) report_status(p.status, GW_ERR_INTERNAL);
       for (int jl = 0; jl < nt; ++jl) {
-        const int j = t0 + jl;
+        const int j = sp + jl * nsplit;
         const uint32_t b = jl & 1;
         const uint32_t n = b ? use1 : use0;
         const uint32_t ws = (tbase + jl) % WSLOTS, wn = (tbase + jl) / WSLOTS;
